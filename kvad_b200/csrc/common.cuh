@@ -1,0 +1,127 @@
+// Shared by every kernel file of kvad_b200: element types, loads that widen to
+// 32-bit, block reductions, and the error convention of the exported C entry
+// points (0 on success; otherwise a negative code and a message that
+// kvad_last_error() returns).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define KVAD_DTYPE_F32 0
+#define KVAD_DTYPE_BF16 1
+
+#define KVAD_OK 0
+#define KVAD_ERR_ARGUMENT (-1)
+#define KVAD_ERR_UNSUPPORTED (-2)
+#define KVAD_ERR_CUDA (-3)
+
+static thread_local char kvad_err_text[768];
+
+#define KVAD_EXPORT extern "C" __attribute__((visibility("default")))
+
+#define KVAD_FAIL(code, ...)                                      \
+  do {                                                            \
+    snprintf(kvad_err_text, sizeof(kvad_err_text), __VA_ARGS__);  \
+    return (code);                                                \
+  } while (0)
+
+#define KVAD_REQUIRE(cond, ...)                                   \
+  do {                                                            \
+    if (!(cond)) KVAD_FAIL(KVAD_ERR_ARGUMENT, __VA_ARGS__);       \
+  } while (0)
+
+#define KVAD_CHECK_LAUNCH(what)                                                    \
+  do {                                                                             \
+    cudaError_t e__ = cudaGetLastError();                                          \
+    if (e__ != cudaSuccess)                                                        \
+      KVAD_FAIL(KVAD_ERR_CUDA, "%s: launch failed: %s", what, cudaGetErrorString(e__)); \
+  } while (0)
+
+#define KVAD_DEFINE_LAST_ERROR()                                  \
+  KVAD_EXPORT const char* kvad_last_error() { return kvad_err_text; }
+
+namespace kvad {
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// A parameter vector (bias, gain) may be stored in 32-bit even when the
+// activations are bfloat16: `is_f32` says which.
+__device__ __forceinline__ float load_param(const void* p, int64_t i, int is_f32) {
+  return is_f32 ? reinterpret_cast<const float*>(p)[i]
+                : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.
+// `scratch` holds 33 floats.  The order of additions depends only on the block
+// size, so a row's result does not depend on what else is in the batch.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n_warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < n_warps ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n_warps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < n_warps ? scratch[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+// tanh-form GELU with bisand/kvad's constants (crates/llm/src/tensor.rs:263-269).
+__device__ __forceinline__ float gelu_tanh(float t) {
+  const float c = 0.79788456f;
+  return 0.5f * t * (1.0f + tanhf(c * (t + 0.044715f * t * t * t)));
+}
+// exact GELU, x * Phi(x), through erf.
+__device__ __forceinline__ float gelu_erf(float t) {
+  return 0.5f * t * (1.0f + erff(t * 0.70710678118654752440f));
+}
+
+// Epilogues of the linear kernels.
+enum Epilogue : int {
+  EPI_STORE = 0,       // out[T]   = acc + bias
+  EPI_GELU_TANH = 1,   // out[T]   = gelu_tanh(acc + bias)
+  EPI_GELU_ERF = 2,    // out[T]   = gelu_erf(acc + bias)
+  EPI_RESIDUAL = 3,    // out[f32] += acc + bias   (the residual stream)
+  EPI_STORE_F32 = 4,   // out[f32] = acc + bias    (logits)
+};
+
+}  // namespace kvad

@@ -1,0 +1,159 @@
+// Row-wise kernels: token (+ position) embedding, LayerNorm, and writing a
+// step's keys and values into the paged cache.  All arithmetic is 32-bit; the
+// element type only says how tensors are stored.
+#include "common.cuh"
+
+using namespace kvad;
+
+// ---------------------------------------------------------------------------
+// x[r, :] = wte[token[r], :] + wpe[position[r], :]        (wpe may be absent)
+// bisand/kvad: crates/llm/src/model/gpt2.rs:200-213.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
+                             const T* __restrict__ wte, const T* __restrict__ wpe,
+                             float* __restrict__ x, int n_rows, int width, int vocab, int n_positions) {
+  const int64_t total = (int64_t)n_rows * width;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / width), c = (int)(i % width);
+    int tok = tokens[r];
+    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);   // ids are checked on the host; this only guards memory
+    float v = to_f32(wte[(int64_t)tok * width + c]);
+    if (wpe != nullptr) {
+      int p = positions[r];
+      p = p < 0 ? 0 : (p >= n_positions ? n_positions - 1 : p);
+      v += to_f32(wpe[(int64_t)p * width + c]);
+    }
+    x[i] = v;
+  }
+}
+
+KVAD_EXPORT int kvad_embed(int dtype, const int* tokens, const int* positions, const void* wte,
+                           const void* wpe, float* x, int n_rows, int width, int vocab,
+                           int n_positions, cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && width > 0 && vocab > 0, "embed: bad sizes rows=%d width=%d vocab=%d", n_rows, width, vocab);
+  KVAD_REQUIRE(wpe == nullptr || n_positions > 0, "embed: a position table needs n_positions > 0");
+  if (n_rows == 0) return KVAD_OK;
+  const int64_t total = (int64_t)n_rows * width;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (dtype == KVAD_DTYPE_F32)
+    embed_kernel<float><<<blocks, threads, 0, stream>>>(tokens, positions, (const float*)wte, (const float*)wpe, x, n_rows, width, vocab, n_positions);
+  else if (dtype == KVAD_DTYPE_BF16)
+    embed_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(tokens, positions, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, x, n_rows, width, vocab, n_positions);
+  else
+    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "embed: unknown dtype %d", dtype);
+  KVAD_CHECK_LAUNCH("embed");
+  return KVAD_OK;
+}
+
+// ---------------------------------------------------------------------------
+// LayerNorm over rows of the 32-bit residual stream, optionally through a row
+// list (the head only normalises the rows whose logits are wanted).
+//   mean = sum(x)/n; var = sum((x-mean)^2)/n (biased, two passes);
+//   y = (x-mean) * 1/sqrt(var+eps) * gain + bias
+// bisand/kvad: crates/llm/src/tensor.rs:245-255.
+// One block per row; the row is staged in shared memory.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void layernorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
+                                 const void* __restrict__ gain, const void* __restrict__ bias,
+                                 int params_f32, T* __restrict__ out, int width, float eps) {
+  extern __shared__ float row[];
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int64_t src = row_index ? (int64_t)row_index[r] : (int64_t)r;
+  const float* xr = x + src * width;
+  float s = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = xr[c];
+    row[c] = v;
+    s += v;
+  }
+  const float mean = block_sum(s, scratch) / (float)width;
+  float q = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float d = row[c] - mean;
+    q += d * d;
+  }
+  const float var = block_sum(q, scratch) / (float)width;
+  const float inv = 1.0f / sqrtf(var + eps);
+  T* o = out + (int64_t)r * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float g = load_param(gain, c, params_f32);
+    const float b = bias ? load_param(bias, c, params_f32) : 0.f;
+    o[c] = from_f32<T>((row[c] - mean) * inv * g + b);
+  }
+}
+
+KVAD_EXPORT int kvad_layernorm(int out_dtype, const float* x, const int* row_index, const void* gain,
+                               const void* bias, int params_f32, void* out, int n_rows, int width,
+                               float eps, cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && width > 0, "layernorm: bad sizes rows=%d width=%d", n_rows, width);
+  KVAD_REQUIRE(gain != nullptr, "layernorm: no gain");
+  if (n_rows == 0) return KVAD_OK;
+  const size_t smem = (size_t)width * sizeof(float);
+  KVAD_REQUIRE(smem <= 200 * 1024, "layernorm: width %d does not fit shared memory (limit %d)", width, 200 * 1024 / 4);
+  const int threads = width >= 1024 ? 256 : 128;
+  if (out_dtype == KVAD_DTYPE_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    layernorm_kernel<float><<<n_rows, threads, smem, stream>>>(x, row_index, gain, bias, params_f32, (float*)out, width, eps);
+  } else if (out_dtype == KVAD_DTYPE_BF16) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    layernorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, stream>>>(x, row_index, gain, bias, params_f32, (__nv_bfloat16*)out, width, eps);
+  } else {
+    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "layernorm: unknown dtype %d", out_dtype);
+  }
+  KVAD_CHECK_LAUNCH("layernorm");
+  return KVAD_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Keys and values of this step's rows go to their place in the paged cache
+// before any row attends (crates/llm/src/model/gpt2.rs:237-242).
+// Cache pages of one layer: [n_pages, n_kv_heads, page_size, head_dim].
+// Row r belongs to sequence row_seq[r] and sits at position row_pos[r]; the
+// sequence's pages are page_table[row_seq[r], :].
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void kv_store_kernel(const T* __restrict__ k_src, const T* __restrict__ v_src, int64_t ld_src,
+                                const int* __restrict__ row_seq, const int* __restrict__ row_pos,
+                                const int* __restrict__ page_table, int table_width,
+                                T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                int n_rows, int n_kv_heads, int head_dim, int page_size) {
+  const int kv_width = n_kv_heads * head_dim;
+  const int64_t total = (int64_t)n_rows * kv_width;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / kv_width), c = (int)(i % kv_width);
+    const int h = c / head_dim, d = c % head_dim;
+    const int pos = row_pos[r];
+    const int page = page_table[(int64_t)row_seq[r] * table_width + pos / page_size];
+    const int64_t dst = (((int64_t)page * n_kv_heads + h) * page_size + pos % page_size) * head_dim + d;
+    k_pages[dst] = k_src[(int64_t)r * ld_src + c];
+    v_pages[dst] = v_src[(int64_t)r * ld_src + c];
+  }
+}
+
+KVAD_EXPORT int kvad_kv_store(int dtype, const void* k_src, const void* v_src, int64_t ld_src,
+                              const int* row_seq, const int* row_pos, const int* page_table,
+                              int table_width, void* k_pages, void* v_pages, int n_rows,
+                              int n_kv_heads, int head_dim, int page_size, cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && n_kv_heads > 0 && head_dim > 0 && page_size > 0 && table_width > 0,
+               "kv_store: bad sizes rows=%d kv_heads=%d head_dim=%d page=%d table=%d", n_rows, n_kv_heads, head_dim, page_size, table_width);
+  if (n_rows == 0) return KVAD_OK;
+  const int64_t total = (int64_t)n_rows * n_kv_heads * head_dim;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (dtype == KVAD_DTYPE_F32)
+    kv_store_kernel<float><<<blocks, threads, 0, stream>>>((const float*)k_src, (const float*)v_src, ld_src, row_seq, row_pos, page_table, table_width, (float*)k_pages, (float*)v_pages, n_rows, n_kv_heads, head_dim, page_size);
+  else if (dtype == KVAD_DTYPE_BF16)
+    kv_store_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)k_src, (const __nv_bfloat16*)v_src, ld_src, row_seq, row_pos, page_table, table_width, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, n_rows, n_kv_heads, head_dim, page_size);
+  else
+    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "kv_store: unknown dtype %d", dtype);
+  KVAD_CHECK_LAUNCH("kv_store");
+  return KVAD_OK;
+}
+
+KVAD_DEFINE_LAST_ERROR()

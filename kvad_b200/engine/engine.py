@@ -1,0 +1,232 @@
+"""The engine: a loaded model, its cache, and ONE step function.
+
+`Engine.step(entries)` is everything between a request's tokens and its next
+token: it runs exactly the tokens it is given - prompts of unequal lengths in
+one step, or one token per sequence - as one packed batch from the cache, and
+returns the 32-bit logits at the wanted places.  Generation, trace replay and
+the benchmark all call it; there is no second forward pass.
+
+bisand/kvad's counterpart is `Session::forward` / `forward_each`
+(crates/llm/src/model/mod.rs:839-976) over `Transformer::{embed, blocks, head}`
+(crates/llm/src/model/gpt2.rs:200-287); the Python entry point has no
+counterpart there and follows the names of `Llm` (crates/llm/src/runtime.rs).
+"""
+from __future__ import annotations
+
+import os
+import sys
+import tempfile
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.device import DeviceCache
+from ..cache.pages import PAGE_SIZE, CacheError, CacheFull
+from ..config import load_config
+from ..models.plan import Model
+from ..ops import KernelError, Ops, lib, libraries_for
+from ..sampling.sampler import SamplingParams
+from ..weights.safetensors_io import Checkpoint
+from ..weights.source import WeightSource
+from .batch import MetaLayout, StepEntry, pack
+from .context import Arena, DeviceMeta, StepContext
+from .generate import Request, Stats, run_all
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "f32": torch.float32}
+
+
+def parse_dtype(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        if name not in (torch.bfloat16, torch.float32):
+            raise ValueError("the engine computes in bfloat16 or float32")
+        return name
+    try:
+        return _DTYPES[str(name).lower()]
+    except KeyError:
+        raise ValueError(f"dtype must be one of {sorted(_DTYPES)}, not `{name}`") from None
+
+
+class Engine:
+    def __init__(self, model: Model, config, *, max_tokens: int = 65536, max_seqs: Optional[int] = None,
+                 verbose: bool = False):
+        if model.dtype is None:
+            raise ValueError("the model has no weights yet")
+        if model.device.type != "cuda":
+            raise KernelError("kvad_b200 runs on a CUDA device; there is no CPU path")
+        self.model = model
+        self.config = config
+        self.dtype = model.dtype
+        self.device = model.device
+        self.vocab_size = model.plan.vocab_size
+        self.max_positions = model.max_positions
+        self.ops = Ops(self.dtype)
+        self.cache = DeviceCache(model.cache_layout, self.dtype, self.device, max_tokens,
+                                 max_seqs=max_seqs, max_positions=self.max_positions, page_size=PAGE_SIZE)
+        self.arena = Arena(self.device, 1 << 20)
+        self._metas: dict[tuple[int, int], DeviceMeta] = {}
+        self._table_widths = {g: self.cache.table_width for g in self.cache.kv_group_ids()}
+        self._sample_bufs = None
+        self.eos_token_ids = tuple(model.plan.eos_token_ids)
+        self.verbose = verbose
+
+    # -- loading -------------------------------------------------------------------
+    @classmethod
+    def from_pretrained(cls, model_dir: str, dtype="bfloat16", *, device="cuda:0", max_tokens: int = 65536,
+                        max_seqs: Optional[int] = None, verbose: bool = False) -> "Engine":
+        """Loads a model folder (config.json + safetensors); the class is chosen by config.json."""
+        tdtype = parse_dtype(dtype)
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device: kvad_b200 has no CPU path")
+        torch.cuda.set_device(torch.device(device))
+        # compile (first call only) what this model needs, before the weights take time
+        from ..csrc import build
+        build.build_all(libraries_for(tdtype), verbose=True)
+        arch, config = load_config(model_dir)
+        model = Model(arch.plan(config))
+        ckpt = Checkpoint.open_dir(model_dir)
+        try:
+            source = WeightSource(ckpt, ignored_suffixes=model.plan.ignored_suffixes)
+            model.load(source, tdtype, device)
+        finally:
+            ckpt.close()
+        gen_cfg = os.path.join(model_dir, "generation_config.json")
+        eng = cls(model, config, max_tokens=max_tokens, max_seqs=max_seqs, verbose=verbose)
+        if os.path.isfile(gen_cfg):
+            from ..config.json_view import JsonView
+            extra = JsonView.from_file(gen_cfg).id_list("eos_token_id")
+            eng.eos_token_ids = tuple(sorted(set(eng.eos_token_ids) | set(extra)))
+        return eng
+
+    @classmethod
+    def random(cls, config, seed: int = 0, dtype="bfloat16", *, model_dir: Optional[str] = None, **kw) -> "Engine":
+        """Random weights: writes a model folder from `config` (a dict in config.json's keys, or a
+        typed configuration) and `seed`, then loads it like any other."""
+        from ..weights.random_init import write_random_model
+        if model_dir is None:
+            with tempfile.TemporaryDirectory(prefix="kvad_b200-random-") as tmp:
+                write_random_model(tmp, config, seed)
+                return cls.from_pretrained(tmp, dtype, **kw)
+        write_random_model(model_dir, config, seed)
+        return cls.from_pretrained(model_dir, dtype, **kw)
+
+    # -- sequences -------------------------------------------------------------------
+    def open(self) -> int:
+        """A slot for a new sequence."""
+        return self.cache.acquire()
+
+    def close(self, slot: int) -> None:
+        """Gives back everything the sequence holds."""
+        self.cache.release(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    def room(self, prompt_len: int) -> int:
+        if self.max_positions is None:
+            return 1 << 30
+        return self.max_positions - prompt_len
+
+    # -- the step ----------------------------------------------------------------------
+    def _meta_for(self, n_rows: int, n_seqs: int) -> DeviceMeta:
+        def bucket(n):
+            b = 16
+            while b < n:
+                b *= 2
+            return b
+        key = (bucket(n_rows), bucket(n_seqs))
+        m = self._metas.get(key)
+        if m is None:
+            m = DeviceMeta(MetaLayout(key[0], key[1], self._table_widths), self.device)
+            self._metas[key] = m
+        return m
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs the given tokens of the given sequences as one batch.
+
+        Returns float32 logits `[wanted rows, vocab]` in the order of the entries
+        and of their `want` lists.  The tensor is scratch: it is valid until the
+        next step.  On an error nothing has changed."""
+        entries = list(entries)
+        for e in entries:
+            if not self.cache.book.slots.is_out(e.slot):
+                raise CacheError(f"slot {e.slot} is not open")
+        firsts = [self.cache.length(e.slot) for e in entries]
+        batch = pack(entries, firsts, self.vocab_size)
+        grown = []
+        try:
+            for e in entries:
+                self.cache.book.grow(e.slot, len(e.tokens))
+                grown.append(e)
+        except CacheError:
+            for e, first in zip(grown, firsts):
+                self.cache.book.truncate(e.slot, first)
+            raise
+        tables = {g: [self.cache.pages_of(e.slot, g) for e in entries] for g in self.cache.kv_group_ids()}
+        meta = self._meta_for(batch.n_rows, batch.n_seqs)
+        meta.upload(batch, tables)
+        self.arena.reset()
+        ctx = StepContext(self.ops, self.cache, self.arena, meta, batch)
+        logits = self.model.forward(ctx)
+        for e in entries:
+            self.cache.book.trim_windows(e.slot)
+        return logits
+
+    # -- sampling on the device ----------------------------------------------------------
+    def sample(self, logits: torch.Tensor, samplers) -> list[int]:
+        """One token per row of `logits`, by each row's own options and stream."""
+        n = logits.shape[0]
+        if self._sample_bufs is None or self._sample_bufs[0].shape[1] < n:
+            cap = max(64, 1 << (n - 1).bit_length())
+            self._sample_bufs = (torch.zeros((4, cap), dtype=torch.float32).pin_memory(),
+                                 torch.zeros((4, cap), dtype=torch.float32, device=self.device),
+                                 torch.zeros(cap, dtype=torch.int32, device=self.device),
+                                 torch.zeros(cap, dtype=torch.int32).pin_memory())
+        host, dev, out, out_host = self._sample_bufs
+        if all(s.params.greedy for s in samplers):
+            self.ops.argmax(logits, out)
+        else:
+            h = host.numpy()
+            for i, s in enumerate(samplers):
+                h[0, i] = s.params.temperature
+                h[1, i] = s.params.top_p
+                h[2, i] = s.next_uniform()
+            hk = h[3].view(np.int32)
+            for i, s in enumerate(samplers):
+                hk[i] = s.params.top_k
+            dev.copy_(host, non_blocking=True)
+            self.ops.sample(logits, dev[0], dev[3].view(torch.int32), dev[1], dev[2], out)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return out_host[:n].tolist()
+
+    def step_and_sample(self, entries, samplers) -> list[int]:
+        """The generation loop's backend call: last-row logits of each entry, then a token each."""
+        logits = self.step([StepEntry(slot, toks, (len(toks) - 1,)) for slot, toks in entries])
+        return self.sample(logits, samplers)
+
+    # -- generation ------------------------------------------------------------------------
+    def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 256, temperature: float = 0.7,
+                 top_k: int = 40, top_p: float = 0.95, seed: int = 7,
+                 stop_token_ids: Optional[Sequence[int]] = None, batch_size: Optional[int] = None,
+                 return_stats: bool = False):
+        """Continues each prompt (token ids in, token ids out).
+
+        Prompts run in batches of `batch_size` (default: all at once), one batch
+        after another.  `temperature <= 0` is greedy.  Request i draws from its
+        own stream seeded `seed + i`.  A stop token (default: the model's
+        `eos_token_id`s) ends its request and is not part of the output."""
+        stops = frozenset(self.eos_token_ids if stop_token_ids is None else stop_token_ids)
+        reqs = [Request(list(p), max_tokens, SamplingParams(temperature, top_k, top_p, seed + i), stops)
+                for i, p in enumerate(prompts)]
+        stats = run_all(self, reqs, batch_size or max(1, len(reqs)))
+        outs = [r.generated for r in reqs]
+        return (outs, stats) if return_stats else outs
+
+    # -- accounting --------------------------------------------------------------------------
+    def describe(self) -> str:
+        m = self.model
+        return (f"{m.plan.summary}\n{m.param_count() / 1e6:.2f} M parameters, "
+                f"{m.weight_bytes() / 1e6:.1f} MB of weights in {str(self.dtype).replace('torch.', '')}; "
+                f"cache {self.cache.bytes() / 1e6:.1f} MB for {self.cache.max_tokens} tokens "
+                f"({self.cache.layout.bytes_per_token(torch.empty((), dtype=self.dtype).element_size())} B per token)")

@@ -1,0 +1,263 @@
+"""Python face of the CUDA kernels.
+
+One `Ops` object serves one compute dtype (float32 or bfloat16).  Its methods
+check what the kernels assume (device, dtype, contiguity, sizes), pass raw
+pointers and the current CUDA stream to the C entry points, and raise
+`KernelError` with the kernel's own message when an entry point refuses.
+Tensors are torch tensors only as owners of device memory; no torch operator
+computes anything here, and nothing falls back to the CPU.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_int64, c_void_p
+from typing import Optional
+
+import torch
+
+from .csrc import build
+
+F32, BF16 = 0, 1
+EPILOGUES = {"store": 0, "gelu_tanh": 1, "gelu_erf": 2, "residual": 3, "store_f32": 4}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kvad_b200 kernels compute in float32 or bfloat16, not {dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+_SIGNATURES = {
+    "rows": {
+        "kvad_embed": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "kvad_layernorm": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
+        "kvad_kv_store": [c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                          c_int, c_int, c_int, c_int, c_void_p],
+    },
+    "linear_simt": {
+        "kvad_linear_simt": [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int,
+                             c_int, c_void_p],
+    },
+    "linear_tcgen05": {
+        "kvad_linear_tcgen05": [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int,
+                                c_int, c_int, c_void_p],
+        "kvad_linear_tcgen05_status": [],
+    },
+    "attention_simt": {
+        "kvad_attention_simt": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
+                                c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    },
+    "attention_prefill": {
+        "kvad_attention_prefill": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    },
+    "attention_decode": {
+        "kvad_attention_decode": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    },
+    "sampling": {
+        "kvad_sample": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "kvad_argmax": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p],
+    },
+}
+
+_bound: dict[str, ctypes.CDLL] = {}
+
+
+def lib(name: str) -> ctypes.CDLL:
+    """The loaded kernel library `name` with its entry points typed."""
+    hit = _bound.get(name)
+    if hit is not None:
+        return hit
+    handle = build.load(name)
+    for fn, argtypes in _SIGNATURES[name].items():
+        f = getattr(handle, fn)
+        f.argtypes = argtypes
+        f.restype = c_int
+    _bound[name] = handle
+    return handle
+
+
+def libraries_for(dtype: torch.dtype) -> list[str]:
+    """Which kernel libraries a model of this compute dtype loads."""
+    names = ["rows", "linear_simt", "attention_simt", "sampling"]
+    if dtype == torch.bfloat16:
+        names += [n for n in ("linear_tcgen05", "attention_prefill", "attention_decode") if n in build.sources()]
+    return names
+
+
+def _check(status: int, handle: ctypes.CDLL) -> None:
+    if status != 0:
+        raise KernelError(handle.kvad_last_error().decode("utf-8", "replace"))
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kvad_b200 kernels run on CUDA tensors only; there is no CPU path")
+
+
+def _rows_view(t: torch.Tensor, what: str) -> int:
+    """Leading dimension of a 2-D tensor whose rows are contiguous."""
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{what}: needs a 2-D tensor with contiguous rows, got shape {tuple(t.shape)} strides {t.stride()}")
+    return t.stride(0)
+
+
+class Ops:
+    """Kernels bound to one compute dtype."""
+
+    def __init__(self, dtype: torch.dtype):
+        self.dtype = dtype
+        self.code = _code(dtype)
+        self.use_tensor_cores = dtype == torch.bfloat16
+        # set to False to keep the bfloat16 engine on the CUDA-core kernels (tests compare both)
+        self.tensor_core_linear = dtype == torch.bfloat16 and "linear_tcgen05" in build.sources()
+        self.tensor_core_prefill = dtype == torch.bfloat16 and "attention_prefill" in build.sources()
+        self.fast_decode = dtype == torch.bfloat16 and "attention_decode" in build.sources()
+
+    # -- embedding -----------------------------------------------------------------
+    def embed(self, tokens, positions, wte, wpe, out) -> None:
+        _need_cuda(tokens, positions, wte, wpe, out)
+        n, width = out.shape
+        if wte.dtype != self.dtype or (wpe is not None and wpe.dtype != self.dtype):
+            raise KernelError(f"embed: tables must be {self.dtype}")
+        if out.dtype != torch.float32 or not out.is_contiguous() or wte.shape[1] != width:
+            raise KernelError("embed: output must be contiguous float32 of the tables' width")
+        if tokens.dtype != torch.int32 or tokens.numel() < n:
+            raise KernelError("embed: tokens must be int32, one per row")
+        h = lib("rows")
+        _check(h.kvad_embed(self.code, _ptr(tokens), _ptr(positions), _ptr(wte), _ptr(wpe), _ptr(out), n, width,
+                            wte.shape[0], 0 if wpe is None else wpe.shape[0], _stream()), h)
+
+    # -- norms ---------------------------------------------------------------------
+    def layernorm(self, x, gain, bias, eps: float, out, rows=None) -> None:
+        _need_cuda(x, gain, bias, out, rows)
+        n, width = out.shape
+        if x.dtype != torch.float32 or not x.is_contiguous() or x.shape[1] != width:
+            raise KernelError("layernorm: input must be the contiguous float32 residual stream")
+        if out.dtype != self.dtype or not out.is_contiguous():
+            raise KernelError(f"layernorm: output must be contiguous {self.dtype}")
+        if gain.numel() != width or (bias is not None and (bias.numel() != width or bias.dtype != gain.dtype)):
+            raise KernelError("layernorm: gain and bias must have the row's width and one dtype")
+        if rows is None and x.shape[0] < n:
+            raise KernelError("layernorm: fewer input rows than output rows")
+        if rows is not None and (rows.dtype != torch.int32 or rows.numel() < n):
+            raise KernelError("layernorm: row list must be int32, one per output row")
+        params_f32 = 1 if gain.dtype == torch.float32 else 0
+        if not params_f32 and gain.dtype != torch.bfloat16:
+            raise KernelError(f"layernorm: gain must be float32 or bfloat16, not {gain.dtype}")
+        h = lib("rows")
+        _check(h.kvad_layernorm(self.code, _ptr(x), _ptr(rows), _ptr(gain), _ptr(bias), params_f32, _ptr(out), n, width,
+                                float(eps), _stream()), h)
+
+    # -- linear --------------------------------------------------------------------
+    def linear(self, a, weight, bias, out, epilogue: str = "store") -> None:
+        """out = epilogue(a . weight^T + bias); weight is [out_features, in_features]."""
+        _need_cuda(a, weight, bias, out)
+        epi = EPILOGUES[epilogue]
+        lda, ldo = _rows_view(a, "linear input"), _rows_view(out, "linear output")
+        m, k = a.shape
+        n = weight.shape[0]
+        if weight.dim() != 2 or weight.shape[1] != k or not weight.is_contiguous():
+            raise KernelError(f"linear: weight {tuple(weight.shape)} does not take inputs of width {k}")
+        if a.dtype != self.dtype or weight.dtype != self.dtype:
+            raise KernelError(f"linear: input and weight must be {self.dtype}")
+        want_out = torch.float32 if epi >= 3 else self.dtype
+        if out.dtype != want_out or out.shape[0] != m or out.shape[1] != n:
+            raise KernelError(f"linear: output must be {want_out} of shape [{m}, {n}]")
+        bias_f32 = 0
+        if bias is not None:
+            if bias.numel() != n:
+                raise KernelError(f"linear: bias has {bias.numel()} entries for {n} outputs")
+            bias_f32 = 1 if bias.dtype == torch.float32 else 0
+            if not bias_f32 and bias.dtype != torch.bfloat16:
+                raise KernelError(f"linear: bias must be float32 or bfloat16, not {bias.dtype}")
+        if self.tensor_core_linear and tcgen05_takes(a, weight, out, lda, ldo):
+            h = lib("linear_tcgen05")
+            _check(h.kvad_linear_tcgen05(_ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k,
+                                         epi, 0, _stream()), h)
+            return
+        h = lib("linear_simt")
+        _check(h.kvad_linear_simt(self.code, _ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k,
+                                  epi, _stream()), h)
+
+    # -- cache writes and attention --------------------------------------------------
+    def kv_store(self, k_src, v_src, row_seq, row_pos, page_table, k_pages, v_pages) -> None:
+        """Writes rows' keys and values to (sequence, position) in one layer's pages
+        `[n_pages, n_kv_heads, page_size, head_dim]`."""
+        _need_cuda(k_src, v_src, row_seq, row_pos, page_table, k_pages, v_pages)
+        ld = _rows_view(k_src, "kv_store keys")
+        if _rows_view(v_src, "kv_store values") != ld or k_src.shape != v_src.shape:
+            raise KernelError("kv_store: keys and values must be views of one buffer with one row stride")
+        _, n_kv, page, hd = k_pages.shape
+        if k_src.shape[1] != n_kv * hd or k_pages.shape != v_pages.shape:
+            raise KernelError("kv_store: rows do not match the cache's heads")
+        if k_src.dtype != self.dtype or k_pages.dtype != self.dtype or not k_pages.is_contiguous() or not v_pages.is_contiguous():
+            raise KernelError(f"kv_store: rows and pages must be {self.dtype}, pages contiguous")
+        h = lib("rows")
+        _check(h.kvad_kv_store(self.code, _ptr(k_src), _ptr(v_src), ld, _ptr(row_seq), _ptr(row_pos), _ptr(page_table),
+                               page_table.shape[1], _ptr(k_pages), _ptr(v_pages), k_src.shape[0], n_kv, hd, page,
+                               _stream()), h)
+
+    def attention(self, q, out, row_seq, row_pos, page_table, k_pages, v_pages, n_heads: int, scale: float,
+                  window: int = 0) -> None:
+        """Every row attends over its own sequence's cached keys up to its own position
+        (general kernel: any rows, any head size up to 512)."""
+        _need_cuda(q, out, row_seq, row_pos, page_table, k_pages, v_pages)
+        ld_q, ld_o = _rows_view(q, "attention queries"), _rows_view(out, "attention output")
+        _, n_kv, page, hd = k_pages.shape
+        if q.shape[1] != n_heads * hd or out.shape[1] != n_heads * hd or q.shape[0] != out.shape[0]:
+            raise KernelError("attention: queries/output do not match heads x head size")
+        if q.dtype != self.dtype or out.dtype != self.dtype or k_pages.dtype != self.dtype:
+            raise KernelError(f"attention: tensors must be {self.dtype}")
+        h = lib("attention_simt")
+        _check(h.kvad_attention_simt(self.code, _ptr(q), ld_q, _ptr(out), ld_o, _ptr(row_seq), _ptr(row_pos),
+                                     _ptr(page_table), page_table.shape[1], _ptr(k_pages), _ptr(v_pages), q.shape[0],
+                                     n_heads, n_kv, hd, page, float(scale), int(window or 0), _stream()), h)
+
+    # -- sampling ------------------------------------------------------------------
+    def argmax(self, logits, out) -> None:
+        _need_cuda(logits, out)
+        ld = _rows_view(logits, "argmax logits")
+        if logits.dtype != torch.float32 or out.dtype != torch.int32 or out.numel() < logits.shape[0]:
+            raise KernelError("argmax: logits must be float32 and the output int32, one per row")
+        h = lib("sampling")
+        _check(h.kvad_argmax(_ptr(logits), ld, logits.shape[0], logits.shape[1], _ptr(out), _stream()), h)
+
+    def sample(self, logits, temperature, top_k, top_p, uniform, out) -> None:
+        """out[r] = token for row r: greedy where temperature[r] <= 0, else top-k, softmax at
+        temperature, top-p, and the draw uniform[r] in [0, 1)."""
+        _need_cuda(logits, temperature, top_k, top_p, uniform, out)
+        ld = _rows_view(logits, "sample logits")
+        n = logits.shape[0]
+        ok = (logits.dtype == torch.float32 and temperature.dtype == torch.float32 and top_p.dtype == torch.float32
+              and top_k.dtype == torch.int32 and uniform.dtype == torch.float32 and out.dtype == torch.int32
+              and min(temperature.numel(), top_k.numel(), top_p.numel(), uniform.numel(), out.numel()) >= n)
+        if not ok:
+            raise KernelError("sample: needs float32 logits/temperature/top_p/uniform and int32 top_k/out, one per row")
+        h = lib("sampling")
+        _check(h.kvad_sample(_ptr(logits), ld, n, logits.shape[1], _ptr(temperature), _ptr(top_k), _ptr(top_p),
+                             _ptr(uniform), _ptr(out), _stream()), h)
+
+
+def tcgen05_takes(a, weight, out, lda: int, ldo: int) -> bool:
+    """Shapes the tensor-core linear kernel accepts: TMA wants 16-byte aligned
+    bases and row strides (bfloat16: multiples of 8 elements)."""
+    k = a.shape[1]
+    return (k % 8 == 0 and lda % 8 == 0 and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
+            and out.data_ptr() % 16 == 0)

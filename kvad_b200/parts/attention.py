@@ -1,0 +1,68 @@
+"""Causal self-attention over the cache, as a mixer.
+
+One fused projection gives queries, keys and values (`q` first, then `k`,
+then `v`; inside each, heads are contiguous groups of `head_dim` columns -
+crates/llm/src/model/gpt2.rs:235-246, crates/llm/src/model/mod.rs:788-792).
+This step's keys and values are written to the cache before any row attends
+(crates/llm/src/model/gpt2.rs:237-242); each row then attends over its own
+sequence's positions up to its own, scores scaled by `score_scale`
+(1/sqrt(head_dim) in bisand/kvad, crates/llm/src/model/mod.rs:777), softmax
+in 32-bit, and the output projection adds into the residual stream.
+Several query heads may share one key/value head (`n_kv_heads < n_heads`),
+and `window` limits each row to the latest positions.
+
+A call with `writes_cache=False` reads the keys and values another call
+wrote to the same cache entry and adds none of its own.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+from ..cache.layout import KVNeed
+from .base import Mixer, PartSpec, build_part, register_part
+from .linear import Linear
+
+
+class CausalSelfAttention(Mixer):
+    def __init__(self, prefix: str, width: int, n_heads: int, head_dim: int, score_scale: float,
+                 n_kv_heads: Optional[int] = None, window: Optional[int] = None, bias: bool = True,
+                 stored: str = "out_in", qkv_name: str = "qkv.", out_name: str = "out.",
+                 position: Optional[PartSpec] = None):
+        super().__init__(prefix)
+        self.width, self.n_heads, self.head_dim = int(width), int(n_heads), int(head_dim)
+        self.n_kv_heads = int(n_kv_heads) if n_kv_heads else self.n_heads
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError(f"{self.n_heads} heads do not divide into {self.n_kv_heads} key/value heads")
+        if self.head_dim % 16:
+            raise ValueError(f"head size {self.head_dim} is not a multiple of 16")
+        self.score_scale, self.window = float(score_scale), window
+        self.q_width = self.n_heads * self.head_dim
+        self.kv_width = self.n_kv_heads * self.head_dim
+        self.qkv = Linear(prefix + qkv_name, self.width, self.q_width + 2 * self.kv_width, bias=bias, stored=stored)
+        self.out = Linear(prefix + out_name, self.q_width, self.width, bias=bias, stored=stored)
+        self.position = build_part("position", position, prefix) if position is not None else None
+
+    def children(self):
+        return [self.qkv, self.out] + ([self.position] if self.position is not None else [])
+
+    def cache_need(self):
+        return KVNeed(self.n_kv_heads, self.head_dim, self.window)
+
+    def forward(self, ctx, h, residual, call):
+        n = h.shape[0]
+        qkv = ctx.buffer((n, self.q_width + 2 * self.kv_width))
+        self.qkv.forward(ctx, h, qkv)
+        q = qkv[:, : self.q_width]
+        k = qkv[:, self.q_width: self.q_width + self.kv_width]
+        v = qkv[:, self.q_width + self.kv_width:]
+        if self.position is not None:
+            self.position.rotate(ctx, q, k)
+        view = ctx.kv(call.cache)
+        if call.writes_cache:
+            ctx.ops.kv_store(k, v, ctx.row_seq, ctx.row_pos, view.page_table, view.k_pages, view.v_pages)
+        mixed = ctx.buffer((n, self.q_width))
+        ctx.attend(q, mixed, view, self.n_heads, self.score_scale)
+        self.out.forward(ctx, mixed, residual, "residual")
+
+
+register_part("mixer", "causal_attention", CausalSelfAttention)

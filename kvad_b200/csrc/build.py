@@ -33,6 +33,7 @@ LIBRARIES = ("rows", "linear_simt", "attention_simt", "sampling", "linear_tcgen0
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
+_dir_lock = threading.Lock()
 
 
 class BuildError(RuntimeError):
@@ -53,7 +54,17 @@ def _nvcc() -> str:
                      "the CUDA kernels of kvad_b200 cannot be built and there is no other path")
 
 
+_dir_cache: list[str] = []
+
+
 def _build_dir() -> str:
+    with _dir_lock:
+        if not _dir_cache:
+            _dir_cache.append(_find_build_dir())
+        return _dir_cache[0]
+
+
+def _find_build_dir() -> str:
     override = os.environ.get("KVAD_BUILD_DIR")
     candidates = [override] if override else []
     candidates.append(os.path.join(_HERE, "_build"))
@@ -61,7 +72,7 @@ def _build_dir() -> str:
     for d in candidates:
         try:
             os.makedirs(d, exist_ok=True)
-            probe = os.path.join(d, f".write-{os.getpid()}")
+            probe = os.path.join(d, f".write-{os.getpid()}-{threading.get_ident()}")
             with open(probe, "w"):
                 pass
             os.remove(probe)

@@ -141,12 +141,8 @@ class Engine:
             self._metas[key] = m
         return m
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """Runs the given tokens of the given sequences as one batch.
-
-        Returns float32 logits `[wanted rows, vocab]` in the order of the entries
-        and of their `want` lists.  The tensor is scratch: it is valid until the
-        next step.  On an error nothing has changed."""
+    def begin_step(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Checks and packs a step, makes room in the cache, uploads the metadata."""
         entries = list(entries)
         for e in entries:
             if not self.cache.book.slots.is_out(e.slot):
@@ -167,9 +163,23 @@ class Engine:
         meta.upload(batch, tables)
         self.arena.reset()
         ctx = StepContext(self.ops, self.cache, self.arena, meta, batch)
-        logits = self.model.forward(ctx)
-        for e in entries:
+        ctx.entries = entries
+        return ctx
+
+    def end_step(self, ctx: StepContext) -> None:
+        for e in ctx.entries:
             self.cache.book.trim_windows(e.slot)
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs the given tokens of the given sequences as one batch.
+
+        Returns float32 logits `[wanted rows, vocab]` in the order of the entries
+        and of their `want` lists.  The tensor is scratch: it is valid until the
+        next step.  A step that is refused (unknown slot, token outside the
+        vocabulary, full context, full cache) changes nothing."""
+        ctx = self.begin_step(entries)
+        logits = self.model.forward(ctx)
+        self.end_step(ctx)
         return logits
 
     # -- sampling on the device ----------------------------------------------------------

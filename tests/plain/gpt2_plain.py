@@ -39,6 +39,8 @@ def read_safetensors(path):
             a = (np.frombuffer(raw, dtype="<u2").astype(np.uint32) << 16).view(np.float32).astype(np.float64)
         elif dt == "F16":
             a = np.frombuffer(raw, dtype="<f2").astype(np.float64)
+        elif dt in ("I64", "I32"):
+            a = np.frombuffer(raw, dtype="<i8" if dt == "I64" else "<i4")
         else:
             raise ValueError(f"plain reader: dtype {dt}")
         out[name] = a.reshape(info["shape"])

@@ -1,0 +1,216 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16, under every way of
+cutting the work: whole requests, the last 32 tokens one by one, unequal batches with slot reuse,
+long decoding, the first tokens, and greedy generation through the entry point."""
+import numpy as np
+import pytest
+import torch
+
+from kvad_b200 import StepEntry
+from tests.conftest import TINY, TOL, random_tokens, rel_err
+
+pytestmark = pytest.mark.gpu
+CASES = [(c, d) for c in ("A", "B", "C") for d in ("float32", "bfloat16")]
+
+
+def poison(engine):
+    """Fills the whole cache with NaN: a read outside a sequence's own positions shows at once."""
+    for k, v in engine.cache.kv.values():
+        k.fill_(float("nan"))
+        v.fill_(float("nan"))
+
+
+def lengths_for(cfg):
+    p = cfg["n_positions"]
+    return [1, 5, 17, 64, 65, min(p, 127), p]
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_each_request_alone_and_whole(engines, plains, name, dtype):
+    e, plain, cfg = engines(name, dtype), plains(name, dtype), TINY[name]
+    poison(e)
+    for i, n in enumerate(lengths_for(cfg)):
+        t = random_tokens(100 + i, n, cfg["vocab_size"])
+        slot = e.open()
+        got = e.step([StepEntry(slot, t, range(n))]).cpu().numpy()
+        e.close(slot)
+        assert rel_err(got, plain.logits(t)) < TOL[dtype], (name, dtype, n)
+    e.cache.book.check_all_free()
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_last_32_tokens_one_by_one(engines, plains, name, dtype):
+    e, plain, cfg = engines(name, dtype), plains(name, dtype), TINY[name]
+    poison(e)
+    for i, n in enumerate([33, 70, cfg["n_positions"]]):
+        t = random_tokens(200 + i, n, cfg["vocab_size"])
+        ref = plain.logits(t)
+        slot = e.open()
+        head = n - 32
+        got = [e.step([StepEntry(slot, t[:head], range(head))]).cpu().numpy()]
+        for j in range(head, n):
+            got.append(e.step([StepEntry(slot, [t[j]], [0])]).cpu().numpy())
+        e.close(slot)
+        got = np.concatenate(got)
+        assert rel_err(got[:head], ref[:head]) < TOL[dtype]
+        for j in range(head, n):      # find the first wrong token, not just "something is wrong"
+            assert rel_err(got[j], ref[j]) < TOL[dtype], f"{name} {dtype}: first wrong decoded position {j} of {n}"
+    e.cache.book.check_all_free()
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_unequal_batches_one_after_another(engines, plains, name, dtype):
+    """Prompts of unequal lengths in one step, then one token each; shorter requests end earlier;
+    batch after batch through a cache so small that slots and pages are used again."""
+    cfg = TINY[name]
+    e, plain = engines(name, dtype, max_tokens=512), plains(name, dtype)
+    poison(e)
+    V, P = cfg["vocab_size"], cfg["n_positions"]
+    rng = np.random.default_rng(7)
+    for b in range(4):
+        prompt_lens = [1, 7, 30, 64][: 3 + b % 2] if b % 2 else [5, 11, 17]
+        extra = [int(rng.integers(1, 13)) for _ in prompt_lens]                 # decoded tokens, unequal
+        seqs = [random_tokens(300 + 10 * b + i, min(P, p + x), V) for i, (p, x) in enumerate(zip(prompt_lens, extra))]
+        refs = [plain.logits(t) for t in seqs]
+        slots = [e.open() for _ in seqs]
+        got = e.step([StepEntry(s, t[:p], [p - 1]) for s, t, p in zip(slots, seqs, prompt_lens)]).cpu().numpy()
+        for i, p in enumerate(prompt_lens):
+            assert rel_err(got[i], refs[i][p - 1]) < TOL[dtype], f"batch {b}: end of prompt {i}"
+        live = list(range(len(seqs)))
+        step = 0
+        while True:
+            for i in list(live):
+                if prompt_lens[i] + step >= len(seqs[i]):
+                    e.close(slots[i])                                            # ends earlier; its slot goes back
+                    live.remove(i)
+            if not live:
+                break
+            got = e.step([StepEntry(slots[i], [seqs[i][prompt_lens[i] + step]], [0]) for i in live]).cpu().numpy()
+            for row, i in enumerate(live):
+                pos = prompt_lens[i] + step
+                assert rel_err(got[row], refs[i][pos]) < TOL[dtype], f"batch {b}: request {i} position {pos} (decode step {step})"
+            step += 1
+        e.cache.book.check_all_free()
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("B", "bfloat16")])
+def test_long_decoding(engines, plains, name, dtype):
+    """From a short prompt to the end of the context, one token at a time, two sequences of unequal age."""
+    e, plain, cfg = engines(name, dtype), plains(name, dtype), TINY[name]
+    poison(e)
+    P, V = cfg["n_positions"], cfg["vocab_size"]
+    a, b = random_tokens(401, P, V), random_tokens(402, P - 40, V)
+    ra, rb = plain.logits(a), plain.logits(b)
+    sa, sb = e.open(), e.open()
+    got = e.step([StepEntry(sa, a[:3], [2]), StepEntry(sb, b[:1], [0])]).cpu().numpy()
+    assert rel_err(got[0], ra[2]) < TOL[dtype] and rel_err(got[1], rb[0]) < TOL[dtype]
+    for j in range(P - 3):
+        ents = [StepEntry(sa, [a[3 + j]], [0])]
+        if 1 + j < len(b):
+            ents.append(StepEntry(sb, [b[1 + j]], [0]))
+        elif 1 + j == len(b):
+            e.close(sb)
+        got = e.step(ents).cpu().numpy()
+        assert rel_err(got[0], ra[3 + j]) < TOL[dtype], f"sequence a, position {3 + j}"
+        if len(ents) == 2:
+            assert rel_err(got[1], rb[1 + j]) < TOL[dtype], f"sequence b, position {1 + j}"
+    with pytest.raises(Exception, match="context window"):
+        e.step([StepEntry(sa, [1], [0])])
+    assert e.length(sa) == P                                # the refused step changed nothing
+    e.close(sa)
+    e.cache.book.check_all_free()
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_first_tokens_of_a_sequence(engines, plains, name, dtype):
+    e, plain, cfg = engines(name, dtype), plains(name, dtype), TINY[name]
+    t = random_tokens(500, 4, cfg["vocab_size"])
+    ref = plain.logits(t)
+    slot = e.open()
+    for j in range(4):
+        got = e.step([StepEntry(slot, [t[j]], [0])]).cpu().numpy()
+        assert rel_err(got[0], ref[j]) < TOL[dtype], f"position {j}"
+    e.close(slot)
+    slot = e.open()                                          # wanting nothing is allowed, and wanting the middle
+    assert e.step([StepEntry(slot, t[:2], [])]).shape[0] == 0
+    got = e.step([StepEntry(slot, t[2:], [0])]).cpu().numpy()
+    assert rel_err(got[0], ref[2]) < TOL[dtype]
+    e.close(slot)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_cutting_changes_nothing_in_32_bit(engines, name):
+    """The same positions through different cuts and different company: equal to rounding, far below the
+    distance to the oracle."""
+    e, cfg = engines(name, "float32"), TINY[name]
+    V = cfg["vocab_size"]
+    t, u = random_tokens(600, 90, V), random_tokens(601, 41, V)
+    s = e.open()
+    whole = e.step([StepEntry(s, t, range(90))]).cpu().numpy()
+    e.close(s)
+    s, s2 = e.open(), e.open()
+    parts = [e.step([StepEntry(s, t[:50], range(50)), StepEntry(s2, u, [40])]).cpu().numpy()[:50],
+             e.step([StepEntry(s, t[50:77], range(27))]).cpu().numpy()]
+    for j in range(77, 90):
+        parts.append(e.step([StepEntry(s2, [u[j % 41]], []), StepEntry(s, [t[j]], [0])]).cpu().numpy())
+    e.close(s), e.close(s2)
+    assert rel_err(np.concatenate(parts), whole) < 2e-6
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_greedy_generation_through_the_entry_point(engines, plains, model_dirs, name, dtype):
+    """Engine.generate, greedy, against the oracle: every token the engine chose is (within the dtype's
+    tolerance) the oracle's best continuation of the engine's own prefix."""
+    from tests.plain.gpt2_plain import PlainGpt2
+    e, cfg = engines(name, dtype), TINY[name]
+    oracle = PlainGpt2(model_dirs[name])
+    prompts = [random_tokens(700 + i, n, cfg["vocab_size"]) for i, n in enumerate([5, 11, 17])]
+    outs = e.generate(prompts, max_tokens=8, temperature=0.0)
+    e.cache.book.check_all_free()
+    exact = 0
+    for p, o in zip(prompts, outs):
+        assert len(o) == 8
+        ref = oracle.logits(p + o)
+        for j, tok in enumerate(o):
+            row = ref[len(p) - 1 + j]
+            exact += int(tok == int(np.argmax(row)))
+            assert row.max() - row[tok] <= TOL[dtype] * np.abs(row).max() * 2, f"token {j} of prompt {len(p)}"
+    if dtype == "float32":
+        assert exact == 24
+    # batches one after another give the same tokens as all at once
+    again = e.generate(prompts, max_tokens=8, temperature=0.0, batch_size=2)
+    assert again == outs
+
+
+def test_stop_token_and_unequal_ends(engines, plains):
+    e = engines("A", "float32")
+    p = [random_tokens(800, 6, 512), random_tokens(801, 9, 512)]
+    free = e.generate(p, max_tokens=10, temperature=0.0)
+    stop = free[0][3]
+    outs = e.generate(p, max_tokens=10, temperature=0.0, stop_token_ids=[stop])
+    cut0 = free[0].index(stop)
+    assert outs[0] == free[0][:cut0] and stop not in outs[0]
+    assert outs[1] == (free[1][:free[1].index(stop)] if stop in free[1] else free[1])
+    e.cache.book.check_all_free()
+
+
+def test_refusals_change_nothing(engines):
+    e = engines("A", "float32", max_tokens=128)
+    s = e.open()
+    e.step([StepEntry(s, [1, 2, 3], [])])
+    for bad in ([StepEntry(s, [512], [0])], [StepEntry(s, [], [])], [StepEntry(s, [1], [1])], [StepEntry(99, [1], [0])]):
+        with pytest.raises(Exception):
+            e.step(bad)
+    s2 = e.open()
+    with pytest.raises(Exception, match="cache is full"):
+        e.step([StepEntry(s, [1] * 60, []), StepEntry(s2, [2] * 70, [])])      # 2 pages for s2, only 1 left
+    assert e.length(s) == 3 and e.length(s2) == 0
+    e.close(s), e.close(s2)
+    e.cache.book.check_all_free()
+
+
+def test_no_cpu_path(model_dirs):
+    from kvad_b200.ops import KernelError, Ops
+    ops = Ops(torch.float32)
+    x = torch.zeros(2, 8)
+    with pytest.raises(KernelError, match="no CPU path"):
+        ops.layernorm(x, torch.ones(8), None, 1e-5, torch.zeros(2, 8))

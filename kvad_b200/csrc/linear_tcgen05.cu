@@ -1,0 +1,461 @@
+// out[M,N] = epilogue(A[M,K] . W[N,K]^T + bias) in bfloat16 on the 5th-generation
+// tensor cores of sm_100a: operands come to shared memory by TMA
+// (cp.async.bulk.tensor, 128-byte swizzle), one elected thread issues
+// tcgen05.mma with the accumulator in tensor memory, and four warps read it
+// back with tcgen05.ld for the fused epilogue (bias; GELU; the 32-bit residual
+// sum; 32-bit logits).  Both operands are K-major, which is how activations
+// lie in memory and how the weights are held ([out, in]); a tied output head
+// is the embedding table as it is.
+//
+// One CTA computes one 128 x BN tile; BN (16..256) is chosen so that the grid
+// fills the 148 SMs: wide tiles when there are many rows (prompts), narrow
+// ones when there are few (decoding), where the kernel is a stream of weights
+// and the rows beyond M are zero-filled by TMA at no memory traffic.  For the
+// residual epilogue K may also be split over CTAs, the partial sums meeting in
+// the 32-bit residual stream through atomic adds.
+//
+// Sizes: any M and N (tails are predicated), K a multiple of 8 (a TMA row
+// stride is a multiple of 16 bytes); the K tail of a 64-wide block is zero-
+// filled.  Other shapes are refused with a message, and the caller falls back
+// to the CUDA-core kernel.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out raises a counter
+// that kvad_linear_tcgen05_status() returns, and the CTA goes on to free its
+// tensor memory and return.
+//
+// bisand/kvad's counterpart is its CPU gemm_bt (crates/llm/src/tensor.rs:102-193)
+// and, on its Metal path, the tensor-op matmul behind Proj::Dense
+// (crates/gpu/src/common.rs:67-73).
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+using namespace kvad;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;              // 64 bfloat16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;    // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+constexpr int SMEM_BUDGET = 200 * 1024;
+
+__device__ int g_wait_timeouts = 0;
+
+template <int BN> struct Tile {
+  static constexpr uint32_t A_BYTES = BM * BK * 2;
+  static constexpr uint32_t B_BYTES = BN * BK * 2;
+  static constexpr int STAGES_RAW = SMEM_BUDGET / (A_BYTES + B_BYTES);
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + (2 * STAGES + 1) * 8 + 16 + 1024;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded: gives up after WAIT_LIMIT polls and says so.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  atomicAdd(&g_wait_timeouts, 1);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes,
+// written by TMA with the 128-byte swizzle: groups of 8 rows are 1024 bytes apart.
+__device__ __forceinline__ uint64_t sw128_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);   // start address / 16
+  d |= (uint64_t)1 << 16;                          // leading byte offset: unused for swizzled K-major
+  d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset / 16
+  d |= (uint64_t)1 << 46;                          // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
+  return d;
+}
+
+// bfloat16 x bfloat16 -> float32, both K-major, M = 128, N = BN.
+template <int BN> __device__ __forceinline__ constexpr uint32_t instr_desc() {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  const uint32_t zero = 0;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(zero) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(addr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// One chunk of CH consecutive columns of one output row.
+template <int EPI, int CH>
+__device__ __forceinline__ void store_chunk(const float* v, void* out, int64_t ldo, int row, int col0, int N,
+                                            const void* bias, int bias_f32, bool add_bias, bool atomic) {
+  float x[CH];
+#pragma unroll
+  for (int j = 0; j < CH; ++j) {
+    float t = v[j];
+    if (add_bias && bias != nullptr && col0 + j < N) t += load_param(bias, col0 + j, bias_f32);
+    if (EPI == EPI_GELU_TANH) t = gelu_tanh(t);
+    if (EPI == EPI_GELU_ERF) t = gelu_erf(t);
+    x[j] = t;
+  }
+  const bool full = col0 + CH <= N;
+  if (EPI == EPI_STORE || EPI == EPI_GELU_TANH || EPI == EPI_GELU_ERF) {
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (int64_t)row * ldo + col0;
+    if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < CH; j += 8) {
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(x[j], x[j + 1]), p1 = __floats2bfloat162_rn(x[j + 2], x[j + 3]);
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(x[j + 4], x[j + 5]), p3 = __floats2bfloat162_rn(x[j + 6], x[j + 7]);
+        uint4 q;
+        q.x = *reinterpret_cast<uint32_t*>(&p0); q.y = *reinterpret_cast<uint32_t*>(&p1);
+        q.z = *reinterpret_cast<uint32_t*>(&p2); q.w = *reinterpret_cast<uint32_t*>(&p3);
+        *reinterpret_cast<uint4*>(o + j) = q;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < CH; ++j)
+        if (col0 + j < N) o[j] = __float2bfloat16_rn(x[j]);
+    }
+  } else {
+    float* o = reinterpret_cast<float*>(out) + (int64_t)row * ldo + col0;
+    if (EPI == EPI_RESIDUAL && atomic) {
+#pragma unroll
+      for (int j = 0; j < CH; ++j)
+        if (col0 + j < N) atomicAdd(o + j, x[j]);
+    } else if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < CH; j += 4) {
+        float4 q = make_float4(x[j], x[j + 1], x[j + 2], x[j + 3]);
+        if (EPI == EPI_RESIDUAL) {
+          const float4 old = *reinterpret_cast<float4*>(o + j);
+          q.x += old.x; q.y += old.y; q.z += old.z; q.w += old.w;
+        }
+        *reinterpret_cast<float4*>(o + j) = q;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < CH; ++j)
+        if (col0 + j < N) o[j] = (EPI == EPI_RESIDUAL) ? o[j] + x[j] : x[j];
+    }
+  }
+}
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                      const void* __restrict__ bias, int bias_f32, void* __restrict__ out, int64_t ldo,
+                      int M, int N, int K, int kb_per_split) {
+  using T = Tile<BN>;
+  constexpr int STAGES = T::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* a_tiles = smem;
+  uint8_t* b_tiles = smem + STAGES * T::A_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(b_tiles + STAGES * T::B_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full_bar = empty_bar + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int kb_total = (K + BK - 1) / BK;
+  const int kb_begin = blockIdx.z * kb_per_split;
+  const int kb_end = kb_begin + kb_per_split < kb_total ? kb_begin + kb_per_split : kb_total;
+  const int num_kb = kb_end - kb_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(tmem_full_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, T::TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % STAGES;
+        const uint32_t phase = (i / STAGES) & 1;
+        if (!mbar_wait(&empty_bar[s], phase ^ 1)) break;
+        mbar_expect_tx(&full_bar[s], T::A_BYTES + T::B_BYTES);
+        tma_load_2d(a_tiles + s * T::A_BYTES, &map_a, &full_bar[s], (kb_begin + i) * BK, m0);
+        tma_load_2d(b_tiles + s * T::B_BYTES, &map_w, &full_bar[s], (kb_begin + i) * BK, n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc<BN>();
+      bool ok = true;
+      for (int i = 0; i < num_kb && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t phase = (i / STAGES) & 1;
+        ok = mbar_wait(&full_bar[s], phase);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t a_desc = sw128_desc(smem_u32(a_tiles + s * T::A_BYTES));
+        const uint64_t b_desc = sw128_desc(smem_u32(b_tiles + s * T::B_BYTES));
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          // 16 elements further along K: 32 bytes inside the swizzled row, i.e. 2 in units of 16 bytes
+          umma(tmem_base, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);     // the stage is free again once these MMAs have read it
+      }
+      umma_commit(tmem_full_bar);       // the accumulator is complete once everything issued has run
+    }
+  } else {
+    const int quarter = warp & 3;       // the 32 tensor-memory lanes this warp may read
+    const int row = m0 + quarter * 32 + lane;
+    const bool ok = mbar_wait(tmem_full_bar, 0);
+    tc_fence_after();
+    if (ok) {
+      const bool add_bias = blockIdx.z == 0;
+      const bool atomic = gridDim.z > 1;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        float v[16];
+        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, v);   // all lanes take part
+        if (row < M && n0 + c < N)
+          store_chunk<EPI, 16>(v, out, ldo, row, n0 + c, N, bias, bias_f32, add_bias, atomic);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, T::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side: tensor maps (made once per tensor and shape, then reused) and the launch.
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr; int64_t ld; int rows, cols, box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && ld == o.ld && rows == o.rows && cols == o.cols && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h = h * 1000003u ^ (size_t)k.ld;
+    h = h * 1000003u ^ (size_t)k.rows;
+    h = h * 1000003u ^ (size_t)k.cols;
+    h = h * 1000003u ^ (size_t)k.box_rows;
+    return h;
+  }
+};
+
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+
+// A [rows, cols] bfloat16 matrix with row stride ld, loaded in boxes of box_rows x 64.
+int tensor_map(const void* ptr, int64_t ld, int rows, int cols, int box_rows, CUtensorMap* out) {
+  MapKey key{ptr, ld, rows, cols, box_rows};
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) {
+    *out = it->second;
+    return KVAD_OK;
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) KVAD_FAIL(KVAD_ERR_CUDA, "linear_tcgen05: the driver does not offer cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    KVAD_FAIL(KVAD_ERR_CUDA, "linear_tcgen05: cuTensorMapEncodeTiled failed (%d) for a [%d, %d] matrix with row stride %lld", (int)r, rows, cols, (long long)ld);
+  if (g_maps.size() > 8192) g_maps.clear();
+  g_maps.emplace(key, m);
+  *out = m;
+  return KVAD_OK;
+}
+
+template <int BN, int EPI>
+int launch(const CUtensorMap& ma, const CUtensorMap& mw, const void* bias, int bias_f32, void* out, int64_t ldo,
+           int M, int N, int K, int splits, cudaStream_t stream) {
+  using T = Tile<BN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(linear_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::SMEM);
+    if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "linear_tcgen05: cannot reserve %zu bytes of shared memory: %s", T::SMEM, cudaGetErrorString(e));
+    configured = true;
+  }
+  const int kb_total = (K + BK - 1) / BK;
+  const int kb_per_split = (kb_total + splits - 1) / splits;
+  const int z = (kb_total + kb_per_split - 1) / kb_per_split;
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, z);
+  linear_tcgen05_kernel<BN, EPI><<<grid, NUM_THREADS, T::SMEM, stream>>>(ma, mw, bias, bias_f32, out, ldo, M, N, K, kb_per_split);
+  KVAD_CHECK_LAUNCH("linear_tcgen05");
+  return KVAD_OK;
+}
+
+template <int BN>
+int launch_epi(int epilogue, const CUtensorMap& ma, const CUtensorMap& mw, const void* bias, int bias_f32, void* out,
+               int64_t ldo, int M, int N, int K, int splits, cudaStream_t stream) {
+  switch (epilogue) {
+    case EPI_STORE: return launch<BN, EPI_STORE>(ma, mw, bias, bias_f32, out, ldo, M, N, K, 1, stream);
+    case EPI_GELU_TANH: return launch<BN, EPI_GELU_TANH>(ma, mw, bias, bias_f32, out, ldo, M, N, K, 1, stream);
+    case EPI_GELU_ERF: return launch<BN, EPI_GELU_ERF>(ma, mw, bias, bias_f32, out, ldo, M, N, K, 1, stream);
+    case EPI_RESIDUAL: return launch<BN, EPI_RESIDUAL>(ma, mw, bias, bias_f32, out, ldo, M, N, K, splits, stream);
+    case EPI_STORE_F32: return launch<BN, EPI_STORE_F32>(ma, mw, bias, bias_f32, out, ldo, M, N, K, 1, stream);
+  }
+  KVAD_FAIL(KVAD_ERR_ARGUMENT, "linear_tcgen05: unknown epilogue %d", epilogue);
+}
+
+}  // namespace
+
+// force_bn: 0 lets the kernel choose its tile width; 16, 32, 64, 128 or 256 fixes it (tests).
+// force_splits: 0 lets it choose how many CTAs share K (residual epilogue only); >= 1 fixes it.
+KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, const void* bias, int bias_f32,
+                                    void* out, int64_t ldo, int M, int N, int K, int epilogue, int force,
+                                    cudaStream_t stream) {
+  KVAD_REQUIRE(M >= 0 && N > 0 && K > 0, "linear_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
+  if (K % 8 != 0 || lda % 8 != 0)
+    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "linear_tcgen05: K=%d and the row stride %lld must be multiples of 8 (TMA strides are multiples of 16 bytes)", K, (long long)lda);
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
+    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "linear_tcgen05: operands must start on 16-byte boundaries");
+  KVAD_REQUIRE(lda >= K && ldo >= N, "linear_tcgen05: leading dimensions lda=%lld ldo=%lld too small", (long long)lda, (long long)ldo);
+  KVAD_REQUIRE((M + BM - 1) / BM <= 65535, "linear_tcgen05: M=%d is more rows than one launch takes", M);
+  if (M == 0) return KVAD_OK;
+
+  const int force_bn = force & 0xffff, force_splits = (force >> 16) & 0xff;
+  const int m_tiles = (M + BM - 1) / BM;
+  int bn = force_bn;
+  if (bn == 0) {
+    bn = 16;
+    const int candidates[5] = {256, 128, 64, 32, 16};
+    for (int i = 0; i < 5; ++i) {
+      const int c = candidates[i];
+      if ((int64_t)m_tiles * ((N + c - 1) / c) >= 132) { bn = c; break; }
+    }
+  }
+  KVAD_REQUIRE(bn == 16 || bn == 32 || bn == 64 || bn == 128 || bn == 256, "linear_tcgen05: tile width %d is not one of 16, 32, 64, 128, 256", bn);
+  const int kb_total = (K + BK - 1) / BK;
+  int splits = 1;
+  if (epilogue == EPI_RESIDUAL) {
+    if (force_splits > 0) {
+      splits = force_splits;
+    } else {
+      const int64_t tiles = (int64_t)m_tiles * ((N + bn - 1) / bn);
+      if (tiles < 100 && kb_total >= 4) {
+        splits = (int)((148 + tiles - 1) / tiles);
+        if (splits > kb_total / 2) splits = kb_total / 2;
+        if (splits > 16) splits = 16;
+      }
+    }
+    if (splits > kb_total) splits = kb_total;
+    if (splits < 1) splits = 1;
+  }
+
+  CUtensorMap ma, mw;
+  int rc = tensor_map(A, lda, M, K, BM, &ma);
+  if (rc != KVAD_OK) return rc;
+  rc = tensor_map(W, K, N, K, bn, &mw);
+  if (rc != KVAD_OK) return rc;
+
+  switch (bn) {
+    case 16: return launch_epi<16>(epilogue, ma, mw, bias, bias_f32, out, ldo, M, N, K, splits, stream);
+    case 32: return launch_epi<32>(epilogue, ma, mw, bias, bias_f32, out, ldo, M, N, K, splits, stream);
+    case 64: return launch_epi<64>(epilogue, ma, mw, bias, bias_f32, out, ldo, M, N, K, splits, stream);
+    case 128: return launch_epi<128>(epilogue, ma, mw, bias, bias_f32, out, ldo, M, N, K, splits, stream);
+    default: return launch_epi<256>(epilogue, ma, mw, bias, bias_f32, out, ldo, M, N, K, splits, stream);
+  }
+}
+
+// How many bounded waits have run out since the library was loaded (0 in a healthy run).
+// Synchronises the device.
+KVAD_EXPORT int kvad_linear_tcgen05_status() {
+  int n = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&n, g_wait_timeouts, sizeof(int));
+  if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "linear_tcgen05_status: %s", cudaGetErrorString(e));
+  return n;
+}
+
+KVAD_DEFINE_LAST_ERROR()

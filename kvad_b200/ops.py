@@ -166,8 +166,10 @@ class Ops:
                                 float(eps), _stream()), h)
 
     # -- linear --------------------------------------------------------------------
-    def linear(self, a, weight, bias, out, epilogue: str = "store") -> None:
-        """out = epilogue(a . weight^T + bias); weight is [out_features, in_features]."""
+    def linear(self, a, weight, bias, out, epilogue: str = "store", *, tile: int = 0, splits: int = 0) -> None:
+        """out = epilogue(a . weight^T + bias); weight is [out_features, in_features].
+
+        `tile` and `splits` fix the tensor-core kernel's tile width and K split (0: its own choice)."""
         _need_cuda(a, weight, bias, out)
         epi = EPILOGUES[epilogue]
         lda, ldo = _rows_view(a, "linear input"), _rows_view(out, "linear output")
@@ -190,7 +192,7 @@ class Ops:
         if self.tensor_core_linear and tcgen05_takes(a, weight, out, lda, ldo):
             h = lib("linear_tcgen05")
             _check(h.kvad_linear_tcgen05(_ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k,
-                                         epi, 0, _stream()), h)
+                                         epi, (int(tile) & 0xffff) | ((int(splits) & 0xff) << 16), _stream()), h)
             return
         h = lib("linear_simt")
         _check(h.kvad_linear_simt(self.code, _ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k,
@@ -253,6 +255,15 @@ class Ops:
         h = lib("sampling")
         _check(h.kvad_sample(_ptr(logits), ld, n, logits.shape[1], _ptr(temperature), _ptr(top_k), _ptr(top_p),
                              _ptr(uniform), _ptr(out), _stream()), h)
+
+
+def tcgen05_wait_timeouts() -> int:
+    """How many bounded waits of the tensor-core linear kernel have run out (0 in a healthy run)."""
+    h = lib("linear_tcgen05")
+    n = h.kvad_linear_tcgen05_status()
+    if n < 0:
+        raise KernelError(h.kvad_last_error().decode("utf-8", "replace"))
+    return n
 
 
 def tcgen05_takes(a, weight, out, lda: int, ldo: int) -> bool:

@@ -1,0 +1,318 @@
+"""Each kernel alone against a plain reference of the same operation (float64 on the CPU, from the
+same inputs), at sizes other than the engine's: widths and vocabularies that are no power of two,
+head sizes in steps of 16, grouped heads, windows, strided inputs, and inputs made so that a fault
+cannot hide (one far key whose score stands out, a window's edge)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from kvad_b200.ops import KernelError, Ops
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+# element-wise closeness of a kernel's output to the float64 reference, relative to the largest value
+KTOL = {"float32": 3e-6, "bfloat16": 6e-3}
+
+
+def dev(t):
+    return t.to("cuda")
+
+
+def rel(got, ref):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    assert torch.isfinite(got).all()
+    return float((got - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
+
+
+def gelu_tanh(v):
+    return 0.5 * v * (1 + torch.tanh(math.sqrt(2 / math.pi) * (v + 0.044715 * v ** 3)))
+
+
+def gelu_erf(v):
+    return 0.5 * v * (1 + torch.erf(v / math.sqrt(2)))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width,vocab,npos", [(48, 1031, 77), (1600, 257, 1024), (8, 5, 3)])
+def test_embed(dtype, width, vocab, npos):
+    g = torch.Generator().manual_seed(1)
+    ops = Ops(DT[dtype])
+    wte, wpe = torch.randn(vocab, width, generator=g).to(DT[dtype]), torch.randn(npos, width, generator=g).to(DT[dtype])
+    n = 37
+    tok = torch.randint(0, vocab, (n,), generator=g, dtype=torch.int32)
+    pos = torch.randint(0, npos, (n,), generator=g, dtype=torch.int32)
+    tok[0], tok[1], pos[0], pos[1] = 0, vocab - 1, npos - 1, 0
+    out = torch.full((n, width), float("nan"), device="cuda")
+    ops.embed(dev(tok), dev(pos), dev(wte), dev(wpe), out)
+    assert torch.equal(out.cpu(), wte.float()[tok.long()] + wpe.float()[pos.long()])      # one 32-bit add: exact
+    ops.embed(dev(tok), dev(pos), dev(wte), None, out)
+    assert torch.equal(out.cpu(), wte.float()[tok.long()])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width", [16, 80, 1600, 5000])
+def test_layernorm(dtype, width):
+    g = torch.Generator().manual_seed(2)
+    ops = Ops(DT[dtype])
+    n = 9
+    x = torch.randn(n, width, generator=g) * 3 + 1.5
+    gain, bias = torch.randn(width, generator=g), torch.randn(width, generator=g)
+    eps = 1e-3
+
+    def ref(rows, gn, bs):
+        xr = x.double()[rows]
+        mean = xr.mean(-1, keepdim=True)
+        var = ((xr - mean) ** 2).mean(-1, keepdim=True)
+        return (xr - mean) / torch.sqrt(var + eps) * gn.double() + (bs.double() if bs is not None else 0)
+
+    for params in ("same", "f32"):                       # parameters in the compute dtype, or kept in 32-bit
+        gn = gain.to(DT[dtype]) if params == "same" else gain
+        bs = bias.to(DT[dtype]) if params == "same" else bias
+        out = torch.full((n, width), float("nan"), device="cuda", dtype=DT[dtype])
+        ops.layernorm(dev(x), dev(gn), dev(bs), eps, out)
+        assert rel(out, ref(torch.arange(n), gn, bs)) < KTOL[dtype]
+    rows = torch.tensor([7, 0, 7, 3], dtype=torch.int32)
+    out = torch.full((4, width), float("nan"), device="cuda", dtype=DT[dtype])
+    ops.layernorm(dev(x), dev(gain.to(DT[dtype])), None, eps, out, dev(rows))
+    assert rel(out, ref(rows.long(), gain.to(DT[dtype]), None)) < KTOL[dtype]
+
+
+def linear_case(ops, dtype, m, n, k, epilogue, g, *, bias=True, strided=False, bias_f32=False, **kw):
+    a = torch.randn(m, k + (8 if strided else 0), generator=g).to(DT[dtype])
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(DT[dtype])
+    b = torch.randn(n, generator=g) if bias else None
+    if b is not None and not bias_f32:
+        b = b.to(DT[dtype])
+    a_dev = dev(a)[:, :k] if strided else dev(a)
+    ref = a[:, :k].double() @ w.double().t() + (b.double() if b is not None else 0)
+    if epilogue == "gelu_tanh":
+        ref = gelu_tanh(ref)
+    elif epilogue == "gelu_erf":
+        ref = gelu_erf(ref)
+    if epilogue == "residual":
+        base = torch.randn(m, n, generator=g)
+        out = dev(base.clone())
+        ref = ref + base.double()
+    elif epilogue == "store_f32":
+        out = torch.full((m, n), float("nan"), device="cuda")
+    else:
+        out = torch.full((m, n), float("nan"), device="cuda", dtype=DT[dtype])
+    ops.linear(a_dev, dev(w), None if b is None else dev(b), out, epilogue, **kw)
+    return rel(out, ref)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_linear_cuda_cores(dtype):
+    ops = Ops(DT[dtype])
+    ops.tensor_core_linear = False
+    g = torch.Generator().manual_seed(3)
+    # odd shapes of bisand/kvad's own GEMM test (crates/llm/src/tensor.rs:487-500) and larger ones
+    for m, n, k in [(9, 13, 7), (8, 16, 4), (5, 32, 1), (6, 8, 9), (1, 1031, 200), (130, 70, 333), (64, 64, 16)]:
+        for epi in ("store", "gelu_tanh", "gelu_erf", "residual", "store_f32"):
+            tol = KTOL[dtype] if epi in ("residual", "store_f32") or dtype == "float32" else KTOL[dtype]
+            assert linear_case(ops, dtype, m, n, k, epi, g) < tol, (m, n, k, epi)
+    assert linear_case(ops, dtype, 7, 19, 24, "store", g, bias=False, strided=True) < KTOL[dtype]
+    assert linear_case(ops, dtype, 7, 19, 24, "store_f32", g, bias_f32=True) < KTOL[dtype]
+
+
+def test_linear_is_true_32_bit_and_row_independent():
+    """The 32-bit kernel sums k in order with fused multiply-adds: a row gives the same bits alone and in a batch,
+    and values that a 19-bit (TF32) product would lose survive."""
+    ops = Ops(torch.float32)
+    g = torch.Generator().manual_seed(4)
+    a, w = torch.randn(70, 96, generator=g), torch.randn(50, 96, generator=g)
+    full = torch.empty(70, 50, device="cuda")
+    one = torch.empty(1, 50, device="cuda")
+    ops.linear(dev(a), dev(w), None, full, "store_f32")
+    ops.linear(dev(a[33:34]), dev(w), None, one, "store_f32")
+    assert torch.equal(full[33:34], one)
+    a = torch.full((1, 8), 1.0 + 2.0 ** -20)
+    w = torch.full((1, 8), 1.0 + 2.0 ** -20)
+    out = torch.empty(1, 1, device="cuda")
+    ops.linear(dev(a), dev(w), None, out, "store_f32")
+    assert abs(out.item() - 8 * (1 + 2.0 ** -20) ** 2) < 2e-6        # TF32 would give exactly 8
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 64, 127, 129, 300])
+def test_linear_tensor_cores_shapes(m):
+    ops = Ops(torch.bfloat16)
+    if not ops.tensor_core_linear:
+        pytest.skip("tensor-core linear kernel not built")
+    from kvad_b200.ops import tcgen05_wait_timeouts
+    g = torch.Generator().manual_seed(5 + m)
+    for n, k in [(768, 768), (1000, 96), (50, 320), (2304, 64), (16, 3072), (777, 200), (1031, 1600)]:
+        for epi in ("store", "gelu_tanh", "gelu_erf", "residual", "store_f32"):
+            assert linear_case(ops, "bfloat16", m, n, k, epi, g) < KTOL["bfloat16"], (m, n, k, epi)
+    assert linear_case(ops, "bfloat16", m, 333, 128, "store", g, bias=False, strided=True) < KTOL["bfloat16"]
+    assert linear_case(ops, "bfloat16", m, 333, 128, "residual", g, bias_f32=True) < KTOL["bfloat16"]
+    assert tcgen05_wait_timeouts() == 0
+
+
+@pytest.mark.parametrize("tile", [16, 32, 64, 128, 256])
+def test_linear_tensor_cores_every_tile_and_split(tile):
+    ops = Ops(torch.bfloat16)
+    if not ops.tensor_core_linear:
+        pytest.skip("tensor-core linear kernel not built")
+    from kvad_b200.ops import tcgen05_wait_timeouts
+    g = torch.Generator().manual_seed(50 + tile)
+    for m, n, k in [(5, 1000, 96), (200, 515, 832), (130, 257, 3072)]:
+        for epi in ("store", "gelu_tanh", "residual", "store_f32"):
+            assert linear_case(ops, "bfloat16", m, n, k, epi, g, tile=tile) < KTOL["bfloat16"], (m, n, k, epi)
+        for splits in (1, 2, 3, 7):
+            assert linear_case(ops, "bfloat16", m, n, k, "residual", g, tile=tile, splits=splits) < KTOL["bfloat16"], (m, n, k, splits)
+    assert tcgen05_wait_timeouts() == 0
+
+
+def test_linear_tensor_cores_large_and_fallback():
+    ops = Ops(torch.bfloat16)
+    if not ops.tensor_core_linear:
+        pytest.skip("tensor-core linear kernel not built")
+    g = torch.Generator().manual_seed(6)
+    assert linear_case(ops, "bfloat16", 2048, 2304, 768, "store", g) < KTOL["bfloat16"]
+    assert linear_case(ops, "bfloat16", 2, 50257, 768, "store_f32", g, bias=False) < KTOL["bfloat16"]
+    # K that TMA cannot stride (not a multiple of 8) goes to the CUDA-core kernel: same answer
+    assert linear_case(ops, "bfloat16", 9, 40, 100, "store", g) < KTOL["bfloat16"]
+    assert linear_case(ops, "bfloat16", 9, 40, 7, "gelu_erf", g) < KTOL["bfloat16"]
+
+
+def make_cache(g, dtype, n_seqs, lens, n_kv, hd, page=64, shuffle=True):
+    """Random keys/values per sequence, scattered over shuffled pages; returns both the paged tensors and the dense ones."""
+    pages_per = [-(-l // page) for l in lens]
+    n_pages = sum(pages_per) + 3
+    order = torch.randperm(n_pages, generator=g).tolist() if shuffle else list(range(n_pages))
+    width = max(pages_per)
+    table = torch.full((n_seqs, width), -1, dtype=torch.int32)
+    kp = torch.full((n_pages, n_kv, page, hd), float("nan")).to(DT[dtype])
+    vp = torch.full((n_pages, n_kv, page, hd), float("nan")).to(DT[dtype])
+    ks, vs = [], []
+    it = iter(order)
+    for s, l in enumerate(lens):
+        k = torch.randn(l, n_kv, hd, generator=g).to(DT[dtype])
+        v = torch.randn(l, n_kv, hd, generator=g).to(DT[dtype])
+        ks.append(k), vs.append(v)
+        for p in range(pages_per[s]):
+            pid = next(it)
+            table[s, p] = pid
+            chunk = slice(p * page, min(l, (p + 1) * page))
+            kp[pid, :, : chunk.stop - chunk.start] = k[chunk].transpose(0, 1)
+            vp[pid, :, : chunk.stop - chunk.start] = v[chunk].transpose(0, 1)
+    return table, kp, vp, ks, vs
+
+
+def attention_ref(q, ks, vs, row_seq, row_pos, n_heads, scale, window):
+    n, hd = q.shape[0], ks[0].shape[-1]
+    n_kv = ks[0].shape[1]
+    out = torch.zeros(n, n_heads * hd, dtype=torch.float64)
+    for r in range(n):
+        s, p = int(row_seq[r]), int(row_pos[r])
+        lo = max(0, p - window + 1) if window else 0
+        for h in range(n_heads):
+            kv = h // (n_heads // n_kv)
+            k, v = ks[s][lo:p + 1, kv].double(), vs[s][lo:p + 1, kv].double()
+            w = torch.softmax((k @ q[r, h * hd:(h + 1) * hd].double()) * scale, 0)
+            out[r, h * hd:(h + 1) * hd] = w @ v
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hd,n_heads,n_kv,window", [(16, 4, 4, 0), (48, 6, 2, 0), (80, 3, 1, 0), (128, 2, 2, 50),
+                                                    (256, 2, 1, 0), (32, 5, 5, 64)])
+def test_kv_store_and_attention(dtype, hd, n_heads, n_kv, window):
+    g = torch.Generator().manual_seed(hd + n_heads)
+    ops = Ops(DT[dtype])
+    lens = [200, 1, 65, 130]
+    table, kp, vp, ks, vs = make_cache(g, dtype, 4, lens, n_kv, hd)
+    # rows: the last 3 positions of sequence 0, the only one of sequence 1, all of sequence 2, two of sequence 3
+    rows = [(0, p) for p in (197, 198, 199)] + [(1, 0)] + [(2, p) for p in range(65)] + [(3, 63), (3, 129)]
+    row_seq = torch.tensor([r[0] for r in rows], dtype=torch.int32)
+    row_pos = torch.tensor([r[1] for r in rows], dtype=torch.int32)
+    n = len(rows)
+    # kv_store: write these rows' keys/values from a strided buffer into cleared pages, expect the same pages back
+    qkv = torch.randn(n, (n_heads + 2 * n_kv) * hd + 8, generator=g).to(DT[dtype])
+    qw, kw = n_heads * hd, n_kv * hd
+    for i, (s, p) in enumerate(rows):
+        qkv[i, qw:qw + kw] = ks[s][p].reshape(-1)
+        qkv[i, qw + kw:qw + 2 * kw] = vs[s][p].reshape(-1)
+    kp2, vp2 = kp.clone(), vp.clone()
+    for i, (s, p) in enumerate(rows):
+        kp2[table[s, p // 64], :, p % 64] = 0
+        vp2[table[s, p // 64], :, p % 64] = 0
+    qkv_d, kp_d, vp_d, table_d = dev(qkv), dev(kp2), dev(vp2), dev(table)
+    ops.kv_store(qkv_d[:, qw:qw + kw], qkv_d[:, qw + kw:qw + 2 * kw], dev(row_seq), dev(row_pos), table_d, kp_d, vp_d)
+    same = lambda a, b: torch.equal(torch.nan_to_num(a.float().cpu(), nan=7.0), torch.nan_to_num(b.float(), nan=7.0))
+    assert same(kp_d, kp) and same(vp_d, vp)
+    out = torch.full((n, qw), float("nan"), device="cuda", dtype=DT[dtype])
+    scale = 0.7 / math.sqrt(hd)
+    ops.attention(qkv_d[:, :qw], out, dev(row_seq), dev(row_pos), table_d, kp_d, vp_d, n_heads, scale, window)
+    ref = attention_ref(qkv[:, :qw], ks, vs, row_seq, row_pos, n_heads, scale, window)
+    assert rel(out, ref) < KTOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_finds_one_far_key_and_respects_the_window_edge(dtype):
+    """One key among 700 is made to stand out (its score is ~30 above the rest): the output must be its value.
+    Then a window that ends one short of it must not see it."""
+    g = torch.Generator().manual_seed(9)
+    ops = Ops(DT[dtype])
+    hd, n = 32, 700
+    table, kp, vp, ks, vs = make_cache(g, dtype, 1, [n], 1, hd)
+    far = 3
+    q = torch.randn(1, hd, generator=g).to(DT[dtype])
+    key = (q[0].float() * 30.0 / q[0].float().pow(2).sum()).to(DT[dtype])      # q . key ~ 30
+    ks[0][far, 0] = key
+    ks[0][:, 0][torch.arange(n) != far] *= 0.05
+    vs[0][far, 0] = torch.arange(hd).to(DT[dtype])
+    table, kp, vp, _, _ = rebuild(table, kp, vp, ks, vs)
+    row_seq, row_pos = torch.zeros(1, dtype=torch.int32), torch.tensor([n - 1], dtype=torch.int32)
+    out = torch.empty(1, hd, device="cuda", dtype=DT[dtype])
+    args = (dev(q), out, dev(row_seq), dev(row_pos), dev(table), dev(kp), dev(vp), 1, 1.0)
+    ops.attention(*args, 0)
+    ref = attention_ref(q, ks, vs, row_seq, row_pos, 1, 1.0, 0)
+    assert rel(out, ref) < KTOL[dtype]
+    assert (out.float().cpu()[0] - torch.arange(hd)).abs().max() < 0.05 * hd         # it is that key's value
+    ops.attention(*args, n - far)                                                     # window reaches exactly to `far`
+    assert (out.float().cpu()[0] - torch.arange(hd)).abs().max() < 0.05 * hd
+    ops.attention(*args, n - far - 1)                                                 # one short: gone
+    assert rel(out, attention_ref(q, ks, vs, row_seq, row_pos, 1, 1.0, n - far - 1)) < KTOL[dtype]
+    assert (out.float().cpu()[0] - torch.arange(hd)).abs().max() > 5
+
+
+def rebuild(table, kp, vp, ks, vs, page=64):
+    for s, (k, v) in enumerate(zip(ks, vs)):
+        for p in range(-(-k.shape[0] // page)):
+            chunk = slice(p * page, min(k.shape[0], (p + 1) * page))
+            kp[table[s, p], :, : chunk.stop - chunk.start] = k[chunk].transpose(0, 1)
+            vp[table[s, p], :, : chunk.stop - chunk.start] = v[chunk].transpose(0, 1)
+    return table, kp, vp, ks, vs
+
+
+def test_attention_refuses_what_it_cannot_do():
+    ops = Ops(torch.float32)
+    kp = torch.zeros(2, 3, 64, 16, device="cuda")
+    q = torch.zeros(1, 4 * 16, device="cuda")
+    z = torch.zeros(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(KernelError, match="do not divide"):
+        ops.attention(q, q.clone(), z, z, torch.zeros(1, 1, dtype=torch.int32, device="cuda"), kp, kp, 4, 1.0)
+    kp = torch.zeros(2, 1, 64, 528, device="cuda")
+    q = torch.zeros(1, 528, device="cuda")
+    with pytest.raises(KernelError, match="head size 528"):
+        ops.attention(q, q.clone(), z, z, torch.zeros(1, 1, dtype=torch.int32, device="cuda"), kp, kp, 1, 1.0)
+
+
+def test_argmax_first_of_equals_and_nan():
+    ops = Ops(torch.float32)
+    g = torch.Generator().manual_seed(10)
+    logits = torch.randn(6, 50257, generator=g)
+    logits[1, 40000] = logits[1, 123] = 9.0
+    logits[2, :] = -1.0
+    logits[3, 7] = float("nan")
+    logits[3, 50000] = 8.0
+    logits[4, 50256] = 99.0
+    buf = torch.zeros(6, 50264, device="cuda")                    # a padded leading dimension
+    buf[:, :50257] = dev(logits)
+    out = torch.full((6,), -1, dtype=torch.int32, device="cuda")
+    ops.argmax(buf[:, :50257], out)
+    want = [int(logits[0].argmax()), 123, 0, 50000, 50256, int(logits[5].argmax())]
+    assert out.cpu().tolist() == want

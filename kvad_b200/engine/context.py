@@ -82,17 +82,22 @@ class DeviceMeta:
         self.tables = {g: self.dev[off:off + L.seqs_cap * w].view(L.seqs_cap, w)
                        for (g, off), w in zip(L.tables.items(), L.table_widths.values())}
 
-    def upload(self, batch: HostBatch, tables: dict[int, list[list[int]]]) -> None:
+    def upload(self, batch: HostBatch, tables: dict[int, list[list[int]]], *, keep_tokens: bool = False) -> int:
+        """Copies a packed step to the device (one asynchronous copy from pinned memory); returns the
+        bytes copied.  With `keep_tokens` the token section is left as the device has it: the tokens
+        were put there by the sampling of the step before."""
         i = self._next
         self._next = (i + 1) % self.STAGES
         if self._events[i] is not None:
             self._events[i].synchronize()
         host = self._host[i]
         self.layout.fill(host.numpy(), batch, tables)
-        self.dev.copy_(host, non_blocking=True)
-        ev = torch.cuda.Event()
+        start = self.layout.row_seq if keep_tokens else 0
+        self.dev[start:].copy_(host[start:], non_blocking=True)
+        ev = self._events[i] or torch.cuda.Event()
         ev.record()
         self._events[i] = ev
+        return (self.layout.total - start) * 4
 
 
 class StepContext:

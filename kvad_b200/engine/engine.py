@@ -47,6 +47,45 @@ def parse_dtype(name) -> torch.dtype:
         raise ValueError(f"dtype must be one of {sorted(_DTYPES)}, not `{name}`") from None
 
 
+class _SampleBuffers:
+    """Sampling options of a step's rows (pinned host + device) and the chosen tokens."""
+
+    def __init__(self, cap: int, device):
+        self.host = torch.zeros((4, cap), dtype=torch.float32).pin_memory()
+        self.dev = torch.zeros((4, cap), dtype=torch.float32, device=device)
+        self.out = torch.zeros(cap, dtype=torch.int32, device=device)
+        self.out_host = torch.zeros(cap, dtype=torch.int32).pin_memory()
+
+    def load(self, samplers, engine) -> bool:
+        """Uploads temperature, top-p, this step's uniform draw and top-k per row; True if all rows are greedy."""
+        if all(s.params.greedy for s in samplers):
+            return True
+        h = self.host.numpy()
+        hk = h[3].view(np.int32)
+        for i, s in enumerate(samplers):
+            h[0, i] = s.params.temperature
+            h[1, i] = s.params.top_p
+            h[2, i] = s.next_uniform()
+            hk[i] = s.params.top_k
+        self.dev.copy_(self.host, non_blocking=True)
+        engine.h2d_bytes += self.host.numel() * 4
+        return False
+
+    def read(self, n: int, engine) -> list[int]:
+        self.out_host[:n].copy_(self.out[:n], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        engine.d2h_bytes += 4 * n
+        return self.out_host[:n].tolist()
+
+
+class _DecodePlan:
+    def __init__(self, meta: DeviceMeta, bufs: _SampleBuffers):
+        self.meta, self.bufs = meta, bufs
+        self.graphs: dict = {}
+        self.warmed: dict = {}
+        self.launches: dict = {}
+
+
 class Engine:
     def __init__(self, model: Model, config, *, max_tokens: int = 65536, max_seqs: Optional[int] = None,
                  verbose: bool = False):
@@ -69,6 +108,11 @@ class Engine:
         self._sample_bufs = None
         self.eos_token_ids = tuple(model.plan.eos_token_ids)
         self.verbose = verbose
+        self.use_graphs = True
+        self._decode_plans: dict = {}
+        self.h2d_bytes = 0          # bytes copied host -> device by steps and sampling (for measurement)
+        self.d2h_bytes = 0
+        self.graph_kernels = 0      # kernels of this library run through graph replays
 
     # -- loading -------------------------------------------------------------------
     @classmethod
@@ -141,7 +185,8 @@ class Engine:
             self._metas[key] = m
         return m
 
-    def begin_step(self, entries: Sequence[StepEntry]) -> StepContext:
+    def begin_step(self, entries: Sequence[StepEntry], *, meta: Optional[DeviceMeta] = None,
+                   keep_tokens: bool = False) -> StepContext:
         """Checks and packs a step, makes room in the cache, uploads the metadata."""
         entries = list(entries)
         for e in entries:
@@ -159,8 +204,8 @@ class Engine:
                 self.cache.book.truncate(e.slot, first)
             raise
         tables = {g: [self.cache.pages_of(e.slot, g) for e in entries] for g in self.cache.kv_group_ids()}
-        meta = self._meta_for(batch.n_rows, batch.n_seqs)
-        meta.upload(batch, tables)
+        meta = meta or self._meta_for(batch.n_rows, batch.n_seqs)
+        self.h2d_bytes += meta.upload(batch, tables, keep_tokens=keep_tokens)
         self.arena.reset()
         ctx = StepContext(self.ops, self.cache, self.arena, meta, batch)
         ctx.entries = entries
@@ -183,37 +228,91 @@ class Engine:
         return logits
 
     # -- sampling on the device ----------------------------------------------------------
+    def _sampling_buffers(self, n: int):
+        if self._sample_bufs is None or self._sample_bufs.host.shape[1] < n:
+            cap = max(64, 1 << (n - 1).bit_length())
+            self._sample_bufs = _SampleBuffers(cap, self.device)
+        return self._sample_bufs
+
     def sample(self, logits: torch.Tensor, samplers) -> list[int]:
         """One token per row of `logits`, by each row's own options and stream."""
         n = logits.shape[0]
-        if self._sample_bufs is None or self._sample_bufs[0].shape[1] < n:
-            cap = max(64, 1 << (n - 1).bit_length())
-            self._sample_bufs = (torch.zeros((4, cap), dtype=torch.float32).pin_memory(),
-                                 torch.zeros((4, cap), dtype=torch.float32, device=self.device),
-                                 torch.zeros(cap, dtype=torch.int32, device=self.device),
-                                 torch.zeros(cap, dtype=torch.int32).pin_memory())
-        host, dev, out, out_host = self._sample_bufs
-        if all(s.params.greedy for s in samplers):
-            self.ops.argmax(logits, out)
+        bufs = self._sampling_buffers(n)
+        greedy = bufs.load(samplers, self)
+        self._run_sampler(logits, bufs, greedy)
+        return bufs.read(n, self)
+
+    def _run_sampler(self, logits, bufs, greedy: bool) -> None:
+        if greedy:
+            self.ops.argmax(logits, bufs.out)
         else:
-            h = host.numpy()
-            for i, s in enumerate(samplers):
-                h[0, i] = s.params.temperature
-                h[1, i] = s.params.top_p
-                h[2, i] = s.next_uniform()
-            hk = h[3].view(np.int32)
-            for i, s in enumerate(samplers):
-                hk[i] = s.params.top_k
-            dev.copy_(host, non_blocking=True)
-            self.ops.sample(logits, dev[0], dev[3].view(torch.int32), dev[1], dev[2], out)
-        out_host.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return out_host[:n].tolist()
+            d = bufs.dev
+            self.ops.sample(logits, d[0], d[3].view(torch.int32), d[1], d[2], bufs.out)
 
     def step_and_sample(self, entries, samplers) -> list[int]:
         """The generation loop's backend call: last-row logits of each entry, then a token each."""
+        if self.use_graphs and all(len(toks) == 1 for _, toks in entries):
+            plan = self._decode(entries, samplers)
+            return plan.bufs.read(len(entries), self)
         logits = self.step([StepEntry(slot, toks, (len(toks) - 1,)) for slot, toks in entries])
         return self.sample(logits, samplers)
+
+    # -- decoding through a captured graph -----------------------------------------------
+    def _decode(self, entries, samplers, *, device_fed: bool = False) -> "_DecodePlan":
+        """One token per sequence, then a token chosen for each; leaves the chosen tokens on the device
+        (in `plan.bufs.out`, and in the token section of the plan's metadata, ready to be the next
+        step's input).  The first step of a batch size runs kernel by kernel; the second captures a
+        CUDA graph; later ones replay it: one upload and one launch per step."""
+        from .. import ops as ops_mod
+        n = len(entries)
+        plan = self._decode_plans.get(n)
+        if plan is None:
+            cap = max(16, 1 << (n - 1).bit_length())
+            plan = _DecodePlan(DeviceMeta(MetaLayout(cap, cap, self._table_widths), self.device),
+                               _SampleBuffers(cap, self.device))
+            self._decode_plans[n] = plan
+        ctx = self.begin_step([StepEntry(slot, toks, (0,)) for slot, toks in entries], meta=plan.meta,
+                              keep_tokens=device_fed)
+        greedy = plan.bufs.load(samplers, self)
+        key = (greedy, self.arena.generation)
+        graph = plan.graphs.get(key)
+        if graph is None and plan.warmed.get(key) and self.use_graphs:
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = ops_mod.launch_count()
+            with torch.cuda.graph(graph):
+                self._decode_body(ctx, plan, greedy)
+            plan.launches[key] = ops_mod.launch_count() - before
+            plan.graphs[key] = graph
+        if graph is not None:
+            graph.replay()
+            self.graph_kernels += plan.launches[key]
+        else:
+            self._decode_body(ctx, plan, greedy)
+            plan.warmed[key] = True
+        self.end_step(ctx)
+        return plan
+
+    def _decode_body(self, ctx, plan, greedy: bool) -> None:
+        logits = self.model.forward(ctx)
+        self._run_sampler(logits, plan.bufs, greedy)
+        plan.meta.tokens[:ctx.n_rows].copy_(plan.bufs.out[:ctx.n_rows])
+
+    def decode_run(self, slots: Sequence[int], first_tokens: Sequence[int], steps: int,
+                   samplers=None) -> torch.Tensor:
+        """`steps` decode steps of the given sequences back to back, each step's chosen tokens feeding
+        the next on the device; the host neither waits nor reads in between.  Returns the chosen
+        tokens `[steps, sequences]` (int32, on the device).  Nothing stops a sequence early here;
+        generation with stop tokens goes through `generate`."""
+        from ..sampling.sampler import RequestSampler
+        n = len(slots)
+        samplers = samplers or [RequestSampler(SamplingParams.make_greedy()) for _ in slots]
+        history = torch.empty((steps, n), dtype=torch.int32, device=self.device)
+        for k in range(steps):
+            toks = first_tokens if k == 0 else [0] * n
+            plan = self._decode([(s, [int(t)]) for s, t in zip(slots, toks)], samplers, device_fed=k > 0)
+            history[k].copy_(plan.bufs.out[:n])
+        return history
 
     # -- generation ------------------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 256, temperature: float = 0.7,

@@ -96,9 +96,19 @@ def libraries_for(dtype: torch.dtype) -> list[str]:
     return names
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernels of this library have been launched (or captured into a graph) so far."""
+    return _launches
+
+
 def _check(status: int, handle: ctypes.CDLL) -> None:
+    global _launches
     if status != 0:
         raise KernelError(handle.kvad_last_error().decode("utf-8", "replace"))
+    _launches += 1
 
 
 def _stream() -> c_void_p:

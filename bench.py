@@ -190,6 +190,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--layers", type=int, default=GPT2_SMALL["n_layer"], help="fewer layers than GPT-2 small has (named in config)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profiling)")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64, prefill and e2e (quick runs)")
     args = ap.parse_args()
 
@@ -217,6 +218,7 @@ def main():
     with tempfile.TemporaryDirectory(prefix="kvad_b200-bench-") as d:
         write_random_model(d, cfg, seed=0)
         engine = Engine.from_pretrained(d, args.dtype, max_tokens=max(64, args.batch) * cfg["n_positions"])
+    engine.use_graphs = not args.no_graphs
     print(f"[bench] {engine.describe()}", file=sys.stderr)
 
     main_pt = decode_point(engine, args.batch, args.prompt_len, args.steps, warmup, seed=1, clock=True)

@@ -1,0 +1,255 @@
+// Attention of single-token rows over the paged cache (decoding), split over the keys.
+//
+// A decode step is a stream of cached keys and values: every (sequence, head)
+// reads its whole history once and does two flops per element, so the kernel
+// is built to keep many bytes in flight.  The keys of one (row, head) are cut
+// into `n_splits` contiguous ranges; a CTA of 128 threads serves one (split,
+// head, row): each thread scores one key of a tile of 128 with 16-byte loads,
+// the tile's softmax is folded into a running maximum and sum, and the values
+// are accumulated with the threads arranged as (group of keys) x (8 head
+// dimensions) so that a warp reads whole rows.  With more than one split the
+// CTA leaves an unnormalised partial result, its maximum and its sum in
+// scratch memory and a second, tiny kernel merges them; with one split it
+// writes the output itself.  All arithmetic is 32-bit; the order of operations
+// for a row depends on the number of splits and on nothing else in the batch.
+//
+// Query head h reads key/value head h / (n_heads / n_kv_heads); `window` > 0
+// limits a row to its latest positions.  Head sizes: multiples of 16 up to 128,
+// and 256; others are refused (the caller falls back to the general kernel).
+//
+// bisand/kvad: attend(), crates/llm/src/model/mod.rs:769-819.
+#include "common.cuh"
+
+using namespace kvad;
+
+namespace {
+
+constexpr int DEC_THREADS = 128;
+constexpr int DEC_WARPS = DEC_THREADS / 32;
+
+template <typename T> struct Vec8;
+template <> struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* f) {
+    const uint4 q = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 v = __bfloat1622float2(h[i]);
+      f[2 * i] = v.x;
+      f[2 * i + 1] = v.y;
+    }
+  }
+};
+template <> struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float* f) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+};
+
+// exp in the accuracy the element type deserves: the fast form for bfloat16 data, the exact one for 32-bit.
+template <typename T> __device__ __forceinline__ float exp_for(float x);
+template <> __device__ __forceinline__ float exp_for<__nv_bfloat16>(float x) { return __expf(x); }
+template <> __device__ __forceinline__ float exp_for<float>(float x) { return expf(x); }
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(DEC_THREADS)
+attention_decode_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict__ out, int64_t ld_out,
+                        const int* __restrict__ row_seq, const int* __restrict__ row_pos,
+                        const int* __restrict__ page_table, int table_width,
+                        const T* __restrict__ k_pages, const T* __restrict__ v_pages, float* __restrict__ scratch,
+                        int n_heads, int n_kv_heads, int page_size, int n_splits, float scale, int window) {
+  constexpr int CH = HD / 8;                    // chunks of 8 dimensions per row
+  constexpr int KG = DEC_THREADS / CH;          // groups of keys that accumulate values side by side
+  __shared__ float qs[HD];
+  __shared__ float ps[DEC_THREADS];
+  __shared__ float red[DEC_WARPS + 1];
+  __shared__ __align__(16) float acc_sh[KG * HD];
+
+  const int split = blockIdx.x, h = blockIdx.y, r = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int kvh = h / (n_heads / n_kv_heads);
+  const int pos = row_pos[r];
+  const int* pages = page_table + (int64_t)row_seq[r] * table_width;
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int n_keys = pos - lo + 1;
+  int per = (n_keys + n_splits - 1) / n_splits;
+  per = (per + 63) / 64 * 64;
+  const int t_begin = lo + split * per;
+  const int t_end = (t_begin + per < pos + 1) ? t_begin + per : pos + 1;
+
+  for (int d = tid; d < HD; d += DEC_THREADS) qs[d] = to_f32(q[(int64_t)r * ld_q + (int64_t)h * HD + d]);
+  __syncthreads();
+
+  const int c = tid % CH, kg = tid / CH;        // this thread's slice of the value accumulation
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  float run_max = -INFINITY, run_sum = 0.f;
+
+  for (int t0 = t_begin; t0 < t_end; t0 += DEC_THREADS) {
+    // ---- one key per thread: score
+    const int t = t0 + tid;
+    float s = -INFINITY;
+    if (t < t_end) {
+      const int page = pages[t / page_size];
+      const T* kr = k_pages + (((int64_t)page * n_kv_heads + kvh) * page_size + t % page_size) * HD;
+      float dot = 0.f;
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        float f[8];
+        Vec8<T>::load(kr + j * 8, f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dot = fmaf(qs[j * 8 + i], f[i], dot);
+      }
+      s = dot * scale;
+    }
+    // ---- the tile's maximum, folded into the running one
+    float m = warp_max(s);
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    if (tid == 0) {
+      float mm = red[0];
+#pragma unroll
+      for (int w = 1; w < DEC_WARPS; ++w) mm = fmaxf(mm, red[w]);
+      red[DEC_WARPS] = mm;
+    }
+    __syncthreads();
+    const float new_max = fmaxf(run_max, red[DEC_WARPS]);
+    const float keep = (run_max == -INFINITY) ? 0.f : exp_for<T>(run_max - new_max);
+    const float p = (t < t_end) ? exp_for<T>(s - new_max) : 0.f;
+    ps[tid] = p;
+    float sum = warp_sum(p);
+    __syncthreads();                       // everyone has read red[DEC_WARPS]; ps is complete
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    float tile_sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) tile_sum += red[w];
+    run_sum = run_sum * keep + tile_sum;
+    run_max = new_max;
+
+    // ---- values: thread (kg, c) adds keys kg, kg + KG, ... of the tile into 8 dimensions
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] *= keep;
+    const int n_here = (t_end - t0) < DEC_THREADS ? (t_end - t0) : DEC_THREADS;
+    if (kg < KG) {
+#pragma unroll 4
+      for (int j = kg; j < n_here; j += KG) {
+        const int tj = t0 + j;
+        const int page = pages[tj / page_size];
+        const T* vr = v_pages + (((int64_t)page * n_kv_heads + kvh) * page_size + tj % page_size) * HD + c * 8;
+        float f[8];
+        Vec8<T>::load(vr, f);
+        const float w = ps[j];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = fmaf(w, f[i], acc[i]);
+      }
+    }
+    __syncthreads();                       // ps and red are rewritten by the next tile
+  }
+
+  // ---- sum the key groups, then write the result or the partial
+  if (kg < KG) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc_sh[kg * HD + c * 8 + i] = acc[i];
+  }
+  __syncthreads();
+  for (int d = tid; d < HD; d += DEC_THREADS) {
+    float o = 0.f;
+#pragma unroll
+    for (int g = 0; g < KG; ++g) o += acc_sh[g * HD + d];
+    if (n_splits == 1) {
+      out[(int64_t)r * ld_out + (int64_t)h * HD + d] = from_f32<T>(o / run_sum);
+    } else {
+      float* part = scratch + (((int64_t)r * n_heads + h) * n_splits + split) * (HD + 2);
+      part[d] = o;
+      if (d == 0) {
+        part[HD] = run_max;
+        part[HD + 1] = run_sum;
+      }
+    }
+  }
+}
+
+// Merges the partial results of the splits of one (row, head).
+template <typename T, int HD>
+__global__ void attention_decode_merge_kernel(const float* __restrict__ scratch, T* __restrict__ out, int64_t ld_out,
+                                              int n_heads, int n_splits) {
+  const int r = blockIdx.x, h = blockIdx.y;
+  const float* part = scratch + ((int64_t)r * n_heads + h) * n_splits * (HD + 2);
+  float m = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part[s * (HD + 2) + HD]);
+  float total = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float ms = part[s * (HD + 2) + HD];
+    if (ms != -INFINITY) total += part[s * (HD + 2) + HD + 1] * exp_for<T>(ms - m);
+  }
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float o = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = part[s * (HD + 2) + HD];
+      if (ms != -INFINITY) o += part[s * (HD + 2) + d] * exp_for<T>(ms - m);
+    }
+    out[(int64_t)r * ld_out + (int64_t)h * HD + d] = from_f32<T>(o / total);
+  }
+}
+
+template <typename T, int HD>
+int launch(const void* q, int64_t ld_q, void* out, int64_t ld_out, const int* row_seq, const int* row_pos,
+           const int* page_table, int table_width, const void* k_pages, const void* v_pages, float* scratch,
+           int n_rows, int n_heads, int n_kv_heads, int page_size, int n_splits, float scale, int window,
+           cudaStream_t stream) {
+  dim3 grid(n_splits, n_heads, n_rows);
+  attention_decode_kernel<T, HD><<<grid, DEC_THREADS, 0, stream>>>(
+      (const T*)q, ld_q, (T*)out, ld_out, row_seq, row_pos, page_table, table_width, (const T*)k_pages,
+      (const T*)v_pages, scratch, n_heads, n_kv_heads, page_size, n_splits, scale, window);
+  KVAD_CHECK_LAUNCH("attention_decode");
+  if (n_splits > 1) {
+    attention_decode_merge_kernel<T, HD><<<dim3(n_rows, n_heads), HD < 64 ? 32 : 64, 0, stream>>>(scratch, (T*)out, ld_out, n_heads, n_splits);
+    KVAD_CHECK_LAUNCH("attention_decode_merge");
+  }
+  return KVAD_OK;
+}
+
+}  // namespace
+
+// How many floats of scratch a call needs (0 with one split).
+KVAD_EXPORT int64_t kvad_attention_decode_scratch(int n_rows, int n_heads, int head_dim, int n_splits) {
+  return n_splits > 1 ? (int64_t)n_rows * n_heads * n_splits * (head_dim + 2) : 0;
+}
+
+KVAD_EXPORT int kvad_attention_decode(int dtype, const void* q, int64_t ld_q, void* out, int64_t ld_out,
+                                      const int* row_seq, const int* row_pos, const int* page_table, int table_width,
+                                      const void* k_pages, const void* v_pages, float* scratch, int n_rows, int n_heads,
+                                      int n_kv_heads, int head_dim, int page_size, int n_splits, float scale, int window,
+                                      cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && n_heads > 0 && n_kv_heads > 0 && page_size > 0 && table_width > 0 && n_splits > 0,
+               "attention_decode: bad sizes rows=%d heads=%d kv_heads=%d page=%d splits=%d", n_rows, n_heads, n_kv_heads, page_size, n_splits);
+  KVAD_REQUIRE(n_heads % n_kv_heads == 0, "attention_decode: %d heads do not divide into %d key/value heads", n_heads, n_kv_heads);
+  KVAD_REQUIRE(n_heads <= 65535 && n_rows <= 65535, "attention_decode: %d heads x %d rows are more than one launch takes", n_heads, n_rows);
+  KVAD_REQUIRE(n_splits == 1 || scratch != nullptr, "attention_decode: %d splits need scratch memory", n_splits);
+  KVAD_REQUIRE((ld_q % 8 == 0) && ((reinterpret_cast<uintptr_t>(k_pages) & 15) == 0) && ((reinterpret_cast<uintptr_t>(v_pages) & 15) == 0),
+               "attention_decode: the cache must start on a 16-byte boundary");
+  if (n_rows == 0) return KVAD_OK;
+#define KVAD_DEC_CASE(HD)                                                                                              \
+  case HD:                                                                                                             \
+    if (dtype == KVAD_DTYPE_BF16)                                                                                      \
+      return launch<__nv_bfloat16, HD>(q, ld_q, out, ld_out, row_seq, row_pos, page_table, table_width, k_pages,       \
+                                       v_pages, scratch, n_rows, n_heads, n_kv_heads, page_size, n_splits, scale,      \
+                                       window, stream);                                                                \
+    if (dtype == KVAD_DTYPE_F32)                                                                                       \
+      return launch<float, HD>(q, ld_q, out, ld_out, row_seq, row_pos, page_table, table_width, k_pages, v_pages,      \
+                               scratch, n_rows, n_heads, n_kv_heads, page_size, n_splits, scale, window, stream);      \
+    break;
+  switch (head_dim) {
+    KVAD_DEC_CASE(16) KVAD_DEC_CASE(32) KVAD_DEC_CASE(48) KVAD_DEC_CASE(64) KVAD_DEC_CASE(80) KVAD_DEC_CASE(96)
+    KVAD_DEC_CASE(112) KVAD_DEC_CASE(128) KVAD_DEC_CASE(256)
+    default:
+      KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention_decode: head size %d is not one of 16..128 in steps of 16, or 256", head_dim);
+  }
+#undef KVAD_DEC_CASE
+  KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention_decode: unknown dtype %d", dtype);
+}
+
+KVAD_DEFINE_LAST_ERROR()

@@ -14,6 +14,12 @@
 // residual epilogue K may also be split over CTAs, the partial sums meeting in
 // the 32-bit residual stream through atomic adds.
 //
+// With at most 64 rows (decoding) the roles are swapped: 128 rows of the WEIGHT
+// matrix are the M side of the MMA and the few activation rows its N side, so
+// that a stage of the pipeline is 16 KB of weights and 2-8 KB of activations
+// instead of the other way round, every byte TMA brings is a byte the product
+// needs, and a CTA can keep its whole share of the weights in flight at once.
+//
 // Sizes: any M and N (tails are predicated), K a multiple of 8 (a TMA row
 // stride is a multiple of 16 bytes); the K tail of a 64-wide block is zero-
 // filled.  Other shapes are refused with a message, and the caller falls back
@@ -291,6 +297,133 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 }
 
 // ---------------------------------------------------------------------------------------------
+// The swapped form for M <= MB <= 64 rows: D[n, m] = sum_k W[n, k] A[m, k].
+// One CTA owns 128 rows of W (and, with split K, a range of K); the accumulator has the weight rows
+// in the tensor-memory lanes and the activation rows in its columns, so a warp of the epilogue holds
+// 32 consecutive outputs of one activation row and writes them side by side.
+// ---------------------------------------------------------------------------------------------
+template <int MB> struct SkinnyTile {
+  static constexpr uint32_t W_BYTES = BM * BK * 2;
+  static constexpr uint32_t A_BYTES = MB * BK * 2;
+  static constexpr int STAGES_RAW = SMEM_BUDGET / (W_BYTES + A_BYTES);
+  static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
+  static constexpr int TMEM_COLS = MB < 32 ? 32 : MB;
+  static constexpr size_t SMEM = (size_t)STAGES * (W_BYTES + A_BYTES) + (2 * STAGES + 1) * 8 + 16 + 1024;
+};
+
+template <int MB, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+linear_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                             const void* __restrict__ bias, int bias_f32, void* __restrict__ out, int64_t ldo,
+                             int M, int N, int K, int kb_per_split) {
+  using T = SkinnyTile<MB>;
+  constexpr int STAGES = T::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* w_tiles = smem;
+  uint8_t* a_tiles = smem + STAGES * T::W_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(a_tiles + STAGES * T::A_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full_bar = empty_bar + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BM;
+  const int kb_total = (K + BK - 1) / BK;
+  const int kb_begin = blockIdx.y * kb_per_split;
+  const int kb_end = kb_begin + kb_per_split < kb_total ? kb_begin + kb_per_split : kb_total;
+  const int num_kb = kb_end - kb_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(tmem_full_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, T::TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % STAGES;
+        const uint32_t phase = (i / STAGES) & 1;
+        if (!mbar_wait(&empty_bar[s], phase ^ 1)) break;
+        mbar_expect_tx(&full_bar[s], T::W_BYTES + T::A_BYTES);
+        tma_load_2d(w_tiles + s * T::W_BYTES, &map_w, &full_bar[s], (kb_begin + i) * BK, n0);
+        tma_load_2d(a_tiles + s * T::A_BYTES, &map_a, &full_bar[s], (kb_begin + i) * BK, 0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc<MB>();
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % STAGES;
+        const uint32_t phase = (i / STAGES) & 1;
+        if (!mbar_wait(&full_bar[s], phase)) break;
+        tc_fence_after();
+        const uint64_t w_desc = sw128_desc(smem_u32(w_tiles + s * T::W_BYTES));
+        const uint64_t a_desc = sw128_desc(smem_u32(a_tiles + s * T::A_BYTES));
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k)
+          umma(tmem_base, w_desc + (uint64_t)(k * 2), a_desc + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&empty_bar[s]);
+      }
+      umma_commit(tmem_full_bar);
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int n = n0 + quarter * 32 + lane;
+    const bool ok = mbar_wait(tmem_full_bar, 0);
+    tc_fence_after();
+    if (ok) {
+      const bool atomic = gridDim.y > 1;
+      float b = 0.f;
+      if (blockIdx.y == 0 && bias != nullptr && n < N) b = load_param(bias, n, bias_f32);
+#pragma unroll 1
+      for (int c = 0; c < MB; c += 16) {
+        float v[16];
+        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, v);
+        if (n < N && c < M) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = c + j;
+            if (m < M) {
+              float t = v[j] + b;
+              if (EPI == EPI_GELU_TANH) t = gelu_tanh(t);
+              if (EPI == EPI_GELU_ERF) t = gelu_erf(t);
+              const int64_t o = (int64_t)m * ldo + n;
+              if (EPI == EPI_STORE || EPI == EPI_GELU_TANH || EPI == EPI_GELU_ERF) {
+                reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(t);
+              } else if (EPI == EPI_RESIDUAL) {
+                if (atomic) atomicAdd(reinterpret_cast<float*>(out) + o, t);
+                else reinterpret_cast<float*>(out)[o] += t;
+              } else {
+                reinterpret_cast<float*>(out)[o] = t;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, T::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Host side: tensor maps (made once per tensor and shape, then reused) and the launch.
 // ---------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -389,10 +522,43 @@ int launch_epi(int epilogue, const CUtensorMap& ma, const CUtensorMap& mw, const
   KVAD_FAIL(KVAD_ERR_ARGUMENT, "linear_tcgen05: unknown epilogue %d", epilogue);
 }
 
+template <int MB, int EPI>
+int launch_skinny(const CUtensorMap& ma, const CUtensorMap& mw, const void* bias, int bias_f32, void* out, int64_t ldo,
+                  int M, int N, int K, int splits, cudaStream_t stream) {
+  using T = SkinnyTile<MB>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(linear_tcgen05_skinny_kernel<MB, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::SMEM);
+    if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "linear_tcgen05: cannot reserve %zu bytes of shared memory: %s", T::SMEM, cudaGetErrorString(e));
+    configured = true;
+  }
+  const int kb_total = (K + BK - 1) / BK;
+  const int kb_per_split = (kb_total + splits - 1) / splits;
+  const int z = (kb_total + kb_per_split - 1) / kb_per_split;
+  dim3 grid((N + BM - 1) / BM, z);
+  linear_tcgen05_skinny_kernel<MB, EPI><<<grid, NUM_THREADS, T::SMEM, stream>>>(ma, mw, bias, bias_f32, out, ldo, M, N, K, kb_per_split);
+  KVAD_CHECK_LAUNCH("linear_tcgen05_skinny");
+  return KVAD_OK;
+}
+
+template <int MB>
+int launch_skinny_epi(int epilogue, const CUtensorMap& ma, const CUtensorMap& mw, const void* bias, int bias_f32,
+                      void* out, int64_t ldo, int M, int N, int K, int splits, cudaStream_t stream) {
+  switch (epilogue) {
+    case EPI_STORE: return launch_skinny<MB, EPI_STORE>(ma, mw, bias, bias_f32, out, ldo, M, N, K, 1, stream);
+    case EPI_GELU_TANH: return launch_skinny<MB, EPI_GELU_TANH>(ma, mw, bias, bias_f32, out, ldo, M, N, K, 1, stream);
+    case EPI_GELU_ERF: return launch_skinny<MB, EPI_GELU_ERF>(ma, mw, bias, bias_f32, out, ldo, M, N, K, 1, stream);
+    case EPI_RESIDUAL: return launch_skinny<MB, EPI_RESIDUAL>(ma, mw, bias, bias_f32, out, ldo, M, N, K, splits, stream);
+    case EPI_STORE_F32: return launch_skinny<MB, EPI_STORE_F32>(ma, mw, bias, bias_f32, out, ldo, M, N, K, 1, stream);
+  }
+  KVAD_FAIL(KVAD_ERR_ARGUMENT, "linear_tcgen05: unknown epilogue %d", epilogue);
+}
+
 }  // namespace
 
-// force_bn: 0 lets the kernel choose its tile width; 16, 32, 64, 128 or 256 fixes it (tests).
-// force_splits: 0 lets it choose how many CTAs share K (residual epilogue only); >= 1 fixes it.
+// `force` fixes what the kernel otherwise chooses (tests): bits 0-15 the tile width of the wide
+// form (16, 32, 64, 128 or 256); bits 16-23 how many CTAs share K (residual epilogue only);
+// bits 24-25 the form: 1 wide (activation rows on the M side), 2 swapped (at most 64 rows).
 KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, const void* bias, int bias_f32,
                                     void* out, int64_t ldo, int M, int N, int K, int epilogue, int force,
                                     cudaStream_t stream) {
@@ -405,7 +571,31 @@ KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, c
   KVAD_REQUIRE((M + BM - 1) / BM <= 65535, "linear_tcgen05: M=%d is more rows than one launch takes", M);
   if (M == 0) return KVAD_OK;
 
-  const int force_bn = force & 0xffff, force_splits = (force >> 16) & 0xff;
+  const int force_bn = force & 0xffff, force_splits = (force >> 16) & 0xff, force_path = (force >> 24) & 3;
+  KVAD_REQUIRE(force_path != 2 || M <= 64, "linear_tcgen05: the swapped form takes at most 64 rows, not %d", M);
+  if ((M <= 64 && force_path != 1 && force_bn == 0) || force_path == 2) {
+    // few rows: weights on the M side of the MMA
+    const int mb = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    const int kb_all = (K + BK - 1) / BK;
+    const int tiles = (N + BM - 1) / BM;
+    int sp = 1;
+    if (epilogue == EPI_RESIDUAL) {
+      sp = force_splits > 0 ? force_splits : (148 + tiles - 1) / tiles;
+      if (sp > 16) sp = 16;
+      if (sp > kb_all) sp = kb_all;
+      if (sp < 1) sp = 1;
+    }
+    CUtensorMap ma, mw;
+    int rc = tensor_map(A, lda, M, K, mb, &ma);
+    if (rc != KVAD_OK) return rc;
+    rc = tensor_map(W, K, N, K, BM, &mw);
+    if (rc != KVAD_OK) return rc;
+    switch (mb) {
+      case 16: return launch_skinny_epi<16>(epilogue, ma, mw, bias, bias_f32, out, ldo, M, N, K, sp, stream);
+      case 32: return launch_skinny_epi<32>(epilogue, ma, mw, bias, bias_f32, out, ldo, M, N, K, sp, stream);
+      default: return launch_skinny_epi<64>(epilogue, ma, mw, bias, bias_f32, out, ldo, M, N, K, sp, stream);
+    }
+  }
   const int m_tiles = (M + BM - 1) / BM;
   int bn = force_bn;
   if (bn == 0) {

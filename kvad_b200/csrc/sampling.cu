@@ -291,11 +291,75 @@ argmax_kernel(const float* __restrict__ logits, int64_t ld, int vocab, int* __re
   if (tid == 0) out[r] = winner == 0x7fffffff ? 0 : winner;
 }
 
-KVAD_EXPORT int kvad_argmax(const float* logits, int64_t ld, int n_rows, int vocab, int* out, cudaStream_t stream) {
+// The same in two stages, for few rows of a large vocabulary: many blocks per row each reduce a
+// chunk to one 64-bit key (value bits above, inverted index below, so that the larger key is the
+// larger value and, among equals, the lower index), then one warp per row takes the largest key.
+constexpr int ARGMAX_CHUNK = 2048;
+
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float* __restrict__ logits, int64_t ld, int vocab, unsigned long long* __restrict__ partial,
+                      int n_chunks) {
+  __shared__ unsigned long long keys[8];
+  const int r = blockIdx.y, chunk = blockIdx.x, tid = threadIdx.x;
+  const float* row = logits + (int64_t)r * ld;
+  const int begin = chunk * ARGMAX_CHUNK;
+  const int end = begin + ARGMAX_CHUNK < vocab ? begin + ARGMAX_CHUNK : vocab;
+  unsigned long long best = 0ull;
+  for (int i = begin + tid; i < end; i += 256) {
+    const unsigned long long key = ((unsigned long long)order_key(row[i]) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)i);
+    best = key > best ? key : best;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = other > best ? other : best;
+  }
+  if ((tid & 31) == 0) keys[tid >> 5] = best;
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < 8; ++w) best = keys[w] > best ? keys[w] : best;
+    partial[(int64_t)r * n_chunks + chunk] = best;
+  }
+}
+
+__global__ void __launch_bounds__(32)
+argmax_final_kernel(const unsigned long long* __restrict__ partial, int n_chunks, int* __restrict__ out) {
+  const int r = blockIdx.x;
+  unsigned long long best = 0ull;
+  for (int i = threadIdx.x; i < n_chunks; i += 32) {
+    const unsigned long long key = partial[(int64_t)r * n_chunks + i];
+    best = key > best ? key : best;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = other > best ? other : best;
+  }
+  if (threadIdx.x == 0) out[r] = (int)(0xffffffffu - (uint32_t)(best & 0xffffffffull));
+}
+
+// How many 64-bit words of scratch the two-stage form needs.
+KVAD_EXPORT int64_t kvad_argmax_scratch(int n_rows, int vocab) {
+  return (int64_t)n_rows * ((vocab + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK);
+}
+
+// scratch == nullptr: one block per row.  Otherwise two stages through `scratch`
+// (kvad_argmax_scratch(n_rows, vocab) 64-bit words).
+KVAD_EXPORT int kvad_argmax(const float* logits, int64_t ld, int n_rows, int vocab, int* out,
+                            unsigned long long* scratch, cudaStream_t stream) {
   KVAD_REQUIRE(n_rows >= 0 && vocab > 0 && ld >= vocab, "argmax: bad sizes rows=%d vocab=%d ld=%lld", n_rows, vocab, (long long)ld);
   if (n_rows == 0) return KVAD_OK;
-  argmax_kernel<<<n_rows, 256, 0, stream>>>(logits, ld, vocab, out);
-  KVAD_CHECK_LAUNCH("argmax");
+  if (scratch == nullptr) {
+    argmax_kernel<<<n_rows, 256, 0, stream>>>(logits, ld, vocab, out);
+    KVAD_CHECK_LAUNCH("argmax");
+    return KVAD_OK;
+  }
+  KVAD_REQUIRE(n_rows <= 65535, "argmax: %d rows are more than one launch takes", n_rows);
+  const int n_chunks = (vocab + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
+  argmax_partial_kernel<<<dim3(n_chunks, n_rows), 256, 0, stream>>>(logits, ld, vocab, scratch, n_chunks);
+  KVAD_CHECK_LAUNCH("argmax_partial");
+  argmax_final_kernel<<<n_rows, 32, 0, stream>>>(scratch, n_chunks, out);
+  KVAD_CHECK_LAUNCH("argmax_final");
   return KVAD_OK;
 }
 

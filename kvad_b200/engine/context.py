@@ -134,7 +134,10 @@ class StepContext:
         ops, b = self.ops, self.batch
         hd = view.k_pages.shape[-1]
         if b.is_decode and ops.fast_decode and ops.decode_takes(hd):
-            ops.attention_decode(q, out, self, view, n_heads, scale)
+            splits = ops.decode_splits(self.n_rows, n_heads, view.page_table.shape[1])
+            scratch = self.buffer((self.n_rows * n_heads * splits * (hd + 2),), torch.float32) if splits > 1 else None
+            ops.attention_decode(q, out, self.row_seq, self.row_pos, view.page_table, view.k_pages, view.v_pages,
+                                 n_heads, scale, view.window or 0, n_splits=splits, scratch=scratch)
         elif (not b.is_decode) and ops.tensor_core_prefill and ops.prefill_takes(hd):
             ops.attention_prefill(q, out, self, view, n_heads, scale)
         else:

@@ -55,6 +55,7 @@ class _SampleBuffers:
         self.dev = torch.zeros((4, cap), dtype=torch.float32, device=device)
         self.out = torch.zeros(cap, dtype=torch.int32, device=device)
         self.out_host = torch.zeros(cap, dtype=torch.int32).pin_memory()
+        self.scratch = None                    # of the two-stage argmax
 
     def load(self, samplers, engine) -> bool:
         """Uploads temperature, top-p, this step's uniform draw and top-k per row; True if all rows are greedy."""
@@ -112,7 +113,7 @@ class Engine:
         self._decode_plans: dict = {}
         self.h2d_bytes = 0          # bytes copied host -> device by steps and sampling (for measurement)
         self.d2h_bytes = 0
-        self.graph_kernels = 0      # kernels of this library run through graph replays
+        self.graph_kernels = 0      # kernels of this library run by decode steps (graph replays count their kernels)
 
     # -- loading -------------------------------------------------------------------
     @classmethod
@@ -244,7 +245,12 @@ class Engine:
 
     def _run_sampler(self, logits, bufs, greedy: bool) -> None:
         if greedy:
-            self.ops.argmax(logits, bufs.out)
+            n, vocab = logits.shape
+            need = n * -(-vocab // self.ops.ARGMAX_CHUNK)
+            if bufs.scratch is None or bufs.scratch.numel() < need:
+                bufs.scratch = torch.zeros(max(need, bufs.out.numel() * -(-vocab // self.ops.ARGMAX_CHUNK)),
+                                           dtype=torch.int64, device=self.device)
+            self.ops.argmax(logits, bufs.out, bufs.scratch)
         else:
             d = bufs.dev
             self.ops.sample(logits, d[0], d[3].view(torch.int32), d[1], d[2], bufs.out)
@@ -288,7 +294,9 @@ class Engine:
             graph.replay()
             self.graph_kernels += plan.launches[key]
         else:
+            before = ops_mod.launch_count()
             self._decode_body(ctx, plan, greedy)
+            self.graph_kernels += ops_mod.launch_count() - before
             plan.warmed[key] = True
         self.end_step(ctx)
         return plan

@@ -62,12 +62,13 @@ _SIGNATURES = {
                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     },
     "attention_decode": {
-        "kvad_attention_decode": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "kvad_attention_decode": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
+                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                  c_void_p],
     },
     "sampling": {
         "kvad_sample": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
-        "kvad_argmax": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p],
+        "kvad_argmax": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p],
     },
 }
 
@@ -176,10 +177,12 @@ class Ops:
                                 float(eps), _stream()), h)
 
     # -- linear --------------------------------------------------------------------
-    def linear(self, a, weight, bias, out, epilogue: str = "store", *, tile: int = 0, splits: int = 0) -> None:
+    def linear(self, a, weight, bias, out, epilogue: str = "store", *, tile: int = 0, splits: int = 0,
+               form: str = "auto") -> None:
         """out = epilogue(a . weight^T + bias); weight is [out_features, in_features].
 
-        `tile` and `splits` fix the tensor-core kernel's tile width and K split (0: its own choice)."""
+        `tile`, `splits` and `form` ("wide", "swapped") fix the tensor-core kernel's tile width, K
+        split and operand roles (0 / "auto": its own choice)."""
         _need_cuda(a, weight, bias, out)
         epi = EPILOGUES[epilogue]
         lda, ldo = _rows_view(a, "linear input"), _rows_view(out, "linear output")
@@ -202,7 +205,8 @@ class Ops:
         if self.tensor_core_linear and tcgen05_takes(a, weight, out, lda, ldo):
             h = lib("linear_tcgen05")
             _check(h.kvad_linear_tcgen05(_ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k,
-                                         epi, (int(tile) & 0xffff) | ((int(splits) & 0xff) << 16), _stream()), h)
+                                         epi, (int(tile) & 0xffff) | ((int(splits) & 0xff) << 16)
+                                         | ({"auto": 0, "wide": 1, "swapped": 2}[form] << 24), _stream()), h)
             return
         h = lib("linear_simt")
         _check(h.kvad_linear_simt(self.code, _ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k,
@@ -242,14 +246,60 @@ class Ops:
                                      _ptr(page_table), page_table.shape[1], _ptr(k_pages), _ptr(v_pages), q.shape[0],
                                      n_heads, n_kv, hd, page, float(scale), int(window or 0), _stream()), h)
 
+    DECODE_HEAD_SIZES = (16, 32, 48, 64, 80, 96, 112, 128, 256)
+
+    def decode_takes(self, head_dim: int) -> bool:
+        return head_dim in self.DECODE_HEAD_SIZES
+
+    @staticmethod
+    def decode_splits(n_rows: int, n_heads: int, table_width: int) -> int:
+        """Into how many key ranges a decode step cuts each (row, head): enough CTAs to fill the GPU
+        twice over, at most one range per page.  Depends on the batch's size only, never on lengths."""
+        want = -(-2 * 148 // max(1, n_rows * n_heads))
+        return max(1, min(want, table_width, 32))
+
+    def attention_decode(self, q, out, row_seq, row_pos, page_table, k_pages, v_pages, n_heads: int, scale: float,
+                         window: int = 0, *, n_splits: int = 1, scratch=None) -> None:
+        """Single-token rows over the cache, keys split over CTAs (decode kernel).  `scratch`: float32,
+        `n_rows * n_heads * n_splits * (head_dim + 2)` elements when `n_splits > 1`."""
+        _need_cuda(q, out, row_seq, row_pos, page_table, k_pages, v_pages, scratch)
+        ld_q, ld_o = _rows_view(q, "attention queries"), _rows_view(out, "attention output")
+        _, n_kv, page, hd = k_pages.shape
+        n = q.shape[0]
+        if q.shape[1] != n_heads * hd or out.shape[1] != n_heads * hd or out.shape[0] != n:
+            raise KernelError("attention_decode: queries/output do not match heads x head size")
+        if q.dtype != self.dtype or out.dtype != self.dtype or k_pages.dtype != self.dtype:
+            raise KernelError(f"attention_decode: tensors must be {self.dtype}")
+        if n_splits > 1 and (scratch is None or scratch.dtype != torch.float32
+                             or scratch.numel() < n * n_heads * n_splits * (hd + 2)):
+            raise KernelError("attention_decode: scratch must be float32 with rows x heads x splits x (head_dim + 2) elements")
+        h = lib("attention_decode")
+        _check(h.kvad_attention_decode(self.code, _ptr(q), ld_q, _ptr(out), ld_o, _ptr(row_seq), _ptr(row_pos),
+                                       _ptr(page_table), page_table.shape[1], _ptr(k_pages), _ptr(v_pages),
+                                       _ptr(scratch), n, n_heads, n_kv, hd, page, int(n_splits), float(scale),
+                                       int(window or 0), _stream()), h)
+        if n_splits > 1:
+            global _launches
+            _launches += 1          # the merge kernel
+
     # -- sampling ------------------------------------------------------------------
-    def argmax(self, logits, out) -> None:
-        _need_cuda(logits, out)
+    ARGMAX_CHUNK = 2048
+
+    def argmax(self, logits, out, scratch=None) -> None:
+        """out[r] = first index of the largest logit of row r.  With `scratch` (int64, rows x
+        ceil(vocab / 2048) words) the rows are reduced by many blocks each, in two stages."""
+        _need_cuda(logits, out, scratch)
         ld = _rows_view(logits, "argmax logits")
-        if logits.dtype != torch.float32 or out.dtype != torch.int32 or out.numel() < logits.shape[0]:
+        n, vocab = logits.shape
+        if logits.dtype != torch.float32 or out.dtype != torch.int32 or out.numel() < n:
             raise KernelError("argmax: logits must be float32 and the output int32, one per row")
+        if scratch is not None and (scratch.dtype != torch.int64 or scratch.numel() < n * -(-vocab // self.ARGMAX_CHUNK)):
+            raise KernelError("argmax: scratch must be int64 with rows x ceil(vocab / 2048) words")
         h = lib("sampling")
-        _check(h.kvad_argmax(_ptr(logits), ld, logits.shape[0], logits.shape[1], _ptr(out), _stream()), h)
+        _check(h.kvad_argmax(_ptr(logits), ld, n, vocab, _ptr(out), _ptr(scratch), _stream()), h)
+        if scratch is not None:
+            global _launches
+            _launches += 1
 
     def sample(self, logits, temperature, top_k, top_p, uniform, out) -> None:
         """out[r] = token for row r: greedy where temperature[r] <= 0, else top-k, softmax at

@@ -165,6 +165,25 @@ def test_linear_tensor_cores_every_tile_and_split(tile):
     assert tcgen05_wait_timeouts() == 0
 
 
+@pytest.mark.parametrize("m", [1, 2, 8, 16, 17, 32, 33, 64])
+def test_linear_tensor_cores_swapped_form(m):
+    """Few rows: the weights sit on the M side of the MMA.  Same answers as the wide form, at every split."""
+    ops = Ops(torch.bfloat16)
+    if not ops.tensor_core_linear:
+        pytest.skip("tensor-core linear kernel not built")
+    from kvad_b200.ops import tcgen05_wait_timeouts
+    g = torch.Generator().manual_seed(70 + m)
+    for n, k in [(768, 768), (1000, 96), (50, 320), (2304, 64), (777, 3072), (50257, 768)]:
+        for epi in ("store", "gelu_tanh", "gelu_erf", "residual", "store_f32"):
+            assert linear_case(ops, "bfloat16", m, n, k, epi, g, form="swapped") < KTOL["bfloat16"], (m, n, k, epi)
+        for splits in (1, 2, 5, 16):
+            assert linear_case(ops, "bfloat16", m, n, k, "residual", g, form="swapped", splits=splits) < KTOL["bfloat16"]
+    assert linear_case(ops, "bfloat16", m, 333, 128, "store", g, bias=False, strided=True, form="swapped") < KTOL["bfloat16"]
+    assert linear_case(ops, "bfloat16", m, 333, 128, "store_f32", g, bias_f32=True, form="swapped") < KTOL["bfloat16"]
+    assert linear_case(ops, "bfloat16", m, 333, 128, "store", g, form="wide") < KTOL["bfloat16"]
+    assert tcgen05_wait_timeouts() == 0
+
+
 def test_linear_tensor_cores_large_and_fallback():
     ops = Ops(torch.bfloat16)
     if not ops.tensor_core_linear:
@@ -316,3 +335,58 @@ def test_argmax_first_of_equals_and_nan():
     ops.argmax(buf[:, :50257], out)
     want = [int(logits[0].argmax()), 123, 0, 50000, 50256, int(logits[5].argmax())]
     assert out.cpu().tolist() == want
+    out.fill_(-1)                                                  # the two-stage form agrees
+    ops.argmax(buf[:, :50257], out, torch.zeros(6 * 25, dtype=torch.int64, device="cuda"))
+    assert out.cpu().tolist() == want
+    small = torch.tensor([[1.0, 5.0, 5.0], [float("nan")] * 3], device="cuda")
+    out2 = torch.full((2,), -1, dtype=torch.int32, device="cuda")
+    ops.argmax(small, out2, torch.zeros(2, dtype=torch.int64, device="cuda"))
+    assert out2.cpu().tolist() == [1, 0]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hd,n_heads,n_kv,window", [(16, 4, 4, 0), (48, 6, 2, 0), (64, 12, 12, 0), (80, 3, 1, 0),
+                                                    (128, 2, 2, 50), (256, 2, 1, 0), (32, 5, 5, 64), (112, 2, 2, 0)])
+def test_attention_decode_split_keys(dtype, hd, n_heads, n_kv, window):
+    """The decode kernel at every split count gives what the plain reference gives; sequences of very unequal
+    length share a launch (an empty split, a single key, a page boundary)."""
+    g = torch.Generator().manual_seed(7 * hd + n_heads)
+    ops = Ops(DT[dtype])
+    lens = [700, 1, 64, 65, 130]
+    table, kp, vp, ks, vs = make_cache(g, dtype, len(lens), lens, n_kv, hd)
+    row_seq = torch.arange(len(lens), dtype=torch.int32)
+    row_pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32)
+    q = torch.randn(len(lens), n_heads * hd + 8, generator=g).to(DT[dtype])
+    scale = 0.9 / math.sqrt(hd)
+    ref = attention_ref(q[:, :n_heads * hd], ks, vs, row_seq, row_pos, n_heads, scale, window)
+    q_d = dev(q)[:, :n_heads * hd]
+    for splits in (1, 2, 5, 11):
+        out = torch.full((len(lens), n_heads * hd), float("nan"), device="cuda", dtype=DT[dtype])
+        scratch = torch.full((len(lens) * n_heads * splits * (hd + 2),), float("nan"), device="cuda")
+        ops.attention_decode(q_d, out, dev(row_seq), dev(row_pos), dev(table), dev(kp), dev(vp), n_heads, scale, window,
+                             n_splits=splits, scratch=scratch if splits > 1 else None)
+        assert rel(out, ref) < KTOL[dtype], (splits,)
+    with pytest.raises(KernelError, match="scratch"):
+        ops.attention_decode(q_d, out, dev(row_seq), dev(row_pos), dev(table), dev(kp), dev(vp), n_heads, scale, window,
+                             n_splits=3, scratch=None)
+
+
+def test_attention_decode_finds_one_far_key():
+    g = torch.Generator().manual_seed(19)
+    ops = Ops(torch.bfloat16)
+    hd, n = 64, 1000
+    table, kp, vp, ks, vs = make_cache(g, "bfloat16", 1, [n], 1, hd)
+    far = 70
+    q = torch.randn(1, hd, generator=g).bfloat16()
+    ks[0][far, 0] = (q[0].float() * 30.0 / q[0].float().pow(2).sum()).bfloat16()
+    ks[0][:, 0][torch.arange(n) != far] *= 0.05
+    vs[0][far, 0] = torch.arange(hd).bfloat16()
+    table, kp, vp, _, _ = rebuild(table, kp, vp, ks, vs)
+    row_seq, row_pos = torch.zeros(1, dtype=torch.int32), torch.tensor([n - 1], dtype=torch.int32)
+    for splits in (1, 4, 16):
+        out = torch.empty(1, hd, device="cuda", dtype=torch.bfloat16)
+        scratch = torch.empty(splits * (hd + 2), device="cuda")
+        ops.attention_decode(dev(q), out, dev(row_seq), dev(row_pos), dev(table), dev(kp), dev(vp), 1, 1.0, 0,
+                             n_splits=splits, scratch=scratch)
+        assert (out.float().cpu()[0] - torch.arange(hd)).abs().max() < 0.05 * hd
+    assert not ops.decode_takes(144) and ops.decode_takes(96)

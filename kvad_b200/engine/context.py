@@ -139,7 +139,8 @@ class StepContext:
             ops.attention_decode(q, out, self.row_seq, self.row_pos, view.page_table, view.k_pages, view.v_pages,
                                  n_heads, scale, view.window or 0, n_splits=splits, scratch=scratch)
         elif (not b.is_decode) and ops.tensor_core_prefill and ops.prefill_takes(hd):
-            ops.attention_prefill(q, out, self, view, n_heads, scale)
+            ops.attention_prefill(q, out, self.seq_starts, self.kv_lens, self.n_seqs, b.max_new, view.page_table,
+                                  view.k_pages, view.v_pages, n_heads, scale, view.window or 0)
         else:
             ops.attention(q, out, self.row_seq, self.row_pos, view.page_table, view.k_pages, view.v_pages,
                           n_heads, scale, view.window or 0)

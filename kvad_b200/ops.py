@@ -58,8 +58,8 @@ _SIGNATURES = {
                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     },
     "attention_prefill": {
-        "kvad_attention_prefill": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "kvad_attention_prefill": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                   c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     },
     "attention_decode": {
         "kvad_attention_decode": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
@@ -245,6 +245,27 @@ class Ops:
         _check(h.kvad_attention_simt(self.code, _ptr(q), ld_q, _ptr(out), ld_o, _ptr(row_seq), _ptr(row_pos),
                                      _ptr(page_table), page_table.shape[1], _ptr(k_pages), _ptr(v_pages), q.shape[0],
                                      n_heads, n_kv, hd, page, float(scale), int(window or 0), _stream()), h)
+
+    PREFILL_HEAD_SIZES = (16, 32, 48, 64, 80, 96, 112, 128)
+
+    def prefill_takes(self, head_dim: int) -> bool:
+        return head_dim in self.PREFILL_HEAD_SIZES
+
+    def attention_prefill(self, q, out, seq_starts, kv_lens, n_seqs: int, max_new: int, page_table, k_pages, v_pages,
+                          n_heads: int, scale: float, window: int = 0) -> None:
+        """Rows of sequences packed one after another (`seq_starts`), each sequence's rows being its
+        last positions (`kv_lens` is its length after the step): causal attention on the tensor cores."""
+        _need_cuda(q, out, seq_starts, kv_lens, page_table, k_pages, v_pages)
+        ld_q, ld_o = _rows_view(q, "attention queries"), _rows_view(out, "attention output")
+        _, n_kv, page, hd = k_pages.shape
+        if q.shape[1] != n_heads * hd or out.shape[1] != n_heads * hd or q.shape[0] != out.shape[0]:
+            raise KernelError("attention_prefill: queries/output do not match heads x head size")
+        if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
+            raise KernelError("attention_prefill: tensors must be bfloat16")
+        h = lib("attention_prefill")
+        _check(h.kvad_attention_prefill(_ptr(q), ld_q, _ptr(out), ld_o, _ptr(seq_starts), _ptr(kv_lens), _ptr(page_table),
+                                        page_table.shape[1], _ptr(k_pages), _ptr(v_pages), int(n_seqs), n_heads, n_kv, hd,
+                                        page, int(max_new), float(scale), int(window or 0), _stream()), h)
 
     DECODE_HEAD_SIZES = (16, 32, 48, 64, 80, 96, 112, 128, 256)
 

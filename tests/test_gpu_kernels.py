@@ -390,3 +390,50 @@ def test_attention_decode_finds_one_far_key():
                              n_splits=splits, scratch=scratch)
         assert (out.float().cpu()[0] - torch.arange(hd)).abs().max() < 0.05 * hd
     assert not ops.decode_takes(144) and ops.decode_takes(96)
+
+
+@pytest.mark.parametrize("hd,n_heads,n_kv,window", [(16, 4, 4, 0), (32, 3, 3, 0), (48, 6, 2, 0), (64, 12, 12, 0), (80, 3, 1, 0),
+                                                    (96, 2, 2, 0), (112, 2, 1, 0), (128, 2, 2, 50), (64, 4, 2, 70), (32, 5, 5, 64)])
+def test_attention_prefill_tensor_cores(hd, n_heads, n_kv, window):
+    """Whole prompts, prompts that continue cached positions, a single row and a row count that is no multiple
+    of the tile, in one launch; the pages hold NaN wherever no position lies."""
+    g = torch.Generator().manual_seed(3 * hd + n_heads + window)
+    ops = Ops(torch.bfloat16)
+    lens = [200, 1, 64, 65, 300, 130]                 # lengths after the step
+    new = [200, 1, 64, 65, 37, 129]                   # rows the step brings (the rest was cached before)
+    table, kp, vp, ks, vs = make_cache(g, "bfloat16", len(lens), lens, n_kv, hd)
+    rows = [(s, p) for s, (l, n) in enumerate(zip(lens, new)) for p in range(l - n, l)]
+    row_seq = torch.tensor([r[0] for r in rows], dtype=torch.int32)
+    row_pos = torch.tensor([r[1] for r in rows], dtype=torch.int32)
+    seq_starts = torch.tensor([0] + list(np.cumsum(new)), dtype=torch.int32)
+    kv_lens = torch.tensor(lens, dtype=torch.int32)
+    q = torch.randn(len(rows), n_heads * hd + 8, generator=g).bfloat16()
+    scale = 0.8 / math.sqrt(hd)
+    ref = attention_ref(q[:, :n_heads * hd], ks, vs, row_seq, row_pos, n_heads, scale, window)
+    out = torch.full((len(rows), n_heads * hd), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.attention_prefill(dev(q)[:, :n_heads * hd], out, dev(seq_starts), dev(kv_lens), len(lens), max(new), dev(table),
+                          dev(kp), dev(vp), n_heads, scale, window)
+    assert rel(out, ref) < KTOL["bfloat16"]
+    # the general kernel agrees on the same launch
+    out2 = torch.full_like(out, float("nan"))
+    ops.attention(dev(q)[:, :n_heads * hd], out2, dev(row_seq), dev(row_pos), dev(table), dev(kp), dev(vp), n_heads, scale, window)
+    assert rel(out2, ref) < KTOL["bfloat16"]
+
+
+def test_attention_prefill_finds_one_far_key():
+    g = torch.Generator().manual_seed(29)
+    ops = Ops(torch.bfloat16)
+    hd, n = 64, 900
+    table, kp, vp, ks, vs = make_cache(g, "bfloat16", 1, [n], 1, hd)
+    far = 5
+    q = torch.randn(n, hd, generator=g).bfloat16() * 0.1
+    q[n - 1] = torch.randn(hd, generator=g).bfloat16()
+    ks[0][far, 0] = (q[n - 1].float() * 30.0 / q[n - 1].float().pow(2).sum()).bfloat16()
+    ks[0][:, 0][torch.arange(n) != far] *= 0.05
+    vs[0][far, 0] = torch.arange(hd).bfloat16()
+    table, kp, vp, _, _ = rebuild(table, kp, vp, ks, vs)
+    out = torch.empty(n, hd, device="cuda", dtype=torch.bfloat16)
+    ops.attention_prefill(dev(q), out, dev(torch.tensor([0, n], dtype=torch.int32)), dev(torch.tensor([n], dtype=torch.int32)),
+                          1, n, dev(table), dev(kp), dev(vp), 1, 1.0, 0)
+    assert (out.float().cpu()[n - 1] - torch.arange(hd)).abs().max() < 0.05 * hd
+    assert not ops.prefill_takes(256) and not ops.prefill_takes(24)

@@ -19,6 +19,7 @@
 //
 // bisand/kvad: attend(), crates/llm/src/model/mod.rs:769-819.
 #include "common.cuh"
+#include "attention_decode_noalloc.h"
 
 using namespace kvad;
 
@@ -250,6 +251,53 @@ KVAD_EXPORT int kvad_attention_decode(int dtype, const void* q, int64_t ld_q, vo
   }
 #undef KVAD_DEC_CASE
   KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention_decode: unknown dtype %d", dtype);
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same kernel for callers that cannot allocate (see attention_decode_noalloc.h): the scratch is
+// this file-scope device array.  In host code its name is only a stand-in for the symbol, not a
+// device address, so the address is asked for once per device and that pointer is what the kernel
+// gets.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) float kvad_decode_noalloc_scratch[KVAD_DECODE_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float* g_noalloc_scratch[NOALLOC_MAX_DEVICES] = {nullptr};
+}  // namespace
+
+KVAD_EXPORT int64_t kvad_attention_decode_noalloc_need(int n_rows, int n_heads, int head_dim, int n_splits) {
+  return kvad_attention_decode_scratch(n_rows, n_heads, head_dim, n_splits);
+}
+
+KVAD_EXPORT int kvad_attention_decode_noalloc(int dtype, const void* q, int64_t ld_q, void* out, int64_t ld_out,
+                                              const int* row_seq, const int* row_pos, const int* page_table,
+                                              int table_width, const void* k_pages, const void* v_pages, int n_rows,
+                                              int n_heads, int n_kv_heads, int head_dim, int page_size, int n_splits,
+                                              float scale, int window, cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && n_heads > 0 && head_dim > 0 && n_splits > 0,
+               "attention_decode_noalloc: bad sizes rows=%d heads=%d head_dim=%d splits=%d", n_rows, n_heads, head_dim, n_splits);
+  const int64_t need = kvad_attention_decode_scratch(n_rows, n_heads, head_dim, n_splits);
+  if (need > (int64_t)KVAD_DECODE_NOALLOC_SCRATCH_FLOATS)
+    KVAD_FAIL(KVAD_ERR_ARGUMENT,
+              "attention_decode_noalloc: %d rows x %d heads x %d splits x (%d + 2) = %lld floats of scratch exceed the built-in %d; "
+              "use fewer splits or rows, or kvad_attention_decode with scratch of your own",
+              n_rows, n_heads, n_splits, head_dim, (long long)need, (int)KVAD_DECODE_NOALLOC_SCRATCH_FLOATS);
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "attention_decode_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+  KVAD_REQUIRE(device >= 0 && device < NOALLOC_MAX_DEVICES, "attention_decode_noalloc: device %d is beyond the %d this entry point keeps track of", device, NOALLOC_MAX_DEVICES);
+  if (g_noalloc_scratch[device] == nullptr) {
+    // set-up, once per device, with that device current
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), kvad_decode_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      KVAD_FAIL(KVAD_ERR_CUDA, "attention_decode_noalloc: cudaGetSymbolAddress failed on device %d: %s", device, cudaGetErrorString(e));
+    g_noalloc_scratch[device] = p;
+  }
+  return kvad_attention_decode(dtype, q, ld_q, out, ld_out, row_seq, row_pos, page_table, table_width, k_pages, v_pages,
+                               g_noalloc_scratch[device], n_rows, n_heads, n_kv_heads, head_dim, page_size, n_splits,
+                               scale, window, stream);
 }
 
 KVAD_DEFINE_LAST_ERROR()

@@ -88,12 +88,9 @@ def sources() -> list[str]:
 
 def _digest(name: str) -> str:
     h = hashlib.sha256()
-    for fn in (name + ".cu", "common.cuh"):
+    headers = sorted(fn for fn in os.listdir(_HERE) if fn.endswith((".cuh", ".h")))
+    for fn in (name + ".cu", *headers):
         with open(os.path.join(_HERE, fn), "rb") as f:
-            h.update(f.read())
-    extra = os.path.join(_HERE, name + ".cuh")
-    if os.path.isfile(extra):
-        with open(extra, "rb") as f:
             h.update(f.read())
     h.update(" ".join(_FLAGS).encode())
     return h.hexdigest()[:16]

@@ -133,6 +133,12 @@ def compile_library(name: str, *, verbose: bool = True) -> str:
             pass
         raise BuildError(f"nvcc failed on {name}.cu (exit {proc.returncode}):\n{out}")
     os.replace(tmp, target)
+    for old in os.listdir(os.path.dirname(target)):          # builds of earlier versions of this source
+        if old.startswith(f"libkvad_{name}.") and old.endswith(".so") and old != os.path.basename(target):
+            try:
+                os.remove(os.path.join(os.path.dirname(target), old))
+            except OSError:
+                pass
     if verbose:
         _say(f"compiled {name}.cu in {time.time() - t0:.1f} s")
     return target

@@ -3,15 +3,16 @@
 // A decode step is a stream of cached keys and values: every (sequence, head)
 // reads its whole history once and does two flops per element, so the kernel
 // is built to keep many bytes in flight.  The keys of one (row, head) are cut
-// into `n_splits` contiguous ranges; a CTA of 128 threads serves one (split,
-// head, row): each thread scores one key of a tile of 128 with 16-byte loads,
-// the tile's softmax is folded into a running maximum and sum, and the values
-// are accumulated with the threads arranged as (group of keys) x (8 head
-// dimensions) so that a warp reads whole rows.  With more than one split the
-// CTA leaves an unnormalised partial result, its maximum and its sum in
-// scratch memory and a second, tiny kernel merges them; with one split it
-// writes the output itself.  All arithmetic is 32-bit; the order of operations
-// for a row depends on the number of splits and on nothing else in the batch.
+// into `n_splits` contiguous ranges; a CTA of four warps serves one (split,
+// head, row), each warp walking chunks of 32 keys with a running maximum, sum
+// and output of its own (a lane per key for the scores, 16-byte loads; HD/8
+// lanes per key for the values) and the warps meeting once at the end.  With
+// more than one split the CTA leaves an unnormalised partial result, its
+// maximum and its sum in scratch memory; the CTA that finishes last merges
+// them (or a second, tiny kernel does).  The step's own key and value can be
+// taken straight from the projection's output and written to the cache here.
+// All arithmetic is 32-bit; the order of operations for a row depends on the
+// number of splits and on nothing else in the batch.
 //
 // Query head h reads key/value head h / (n_heads / n_kv_heads); `window` > 0
 // limits a row to its latest positions.  Head sizes: multiples of 16 up to 128,
@@ -53,23 +54,61 @@ template <typename T> __device__ __forceinline__ float exp_for(float x);
 template <> __device__ __forceinline__ float exp_for<__nv_bfloat16>(float x) { return __expf(x); }
 template <> __device__ __forceinline__ float exp_for<float>(float x) { return expf(x); }
 
+// Merges the partial results (unnormalised output, maximum, sum) of the splits of one (row, head).
+template <typename T, int HD>
+__device__ __forceinline__ void merge_partials(const float* part, T* dst, int n_splits,
+                                               int tid, int n_threads) {
+  // other CTAs of this launch may have written the partials: read them past the L1 cache
+  float m = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, __ldcg(part + s * (HD + 2) + HD));
+  float total = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float ms = __ldcg(part + s * (HD + 2) + HD);
+    if (ms != -INFINITY) total += __ldcg(part + s * (HD + 2) + HD + 1) * exp_for<T>(ms - m);
+  }
+  for (int d = tid; d < HD; d += n_threads) {
+    float o = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = __ldcg(part + s * (HD + 2) + HD);
+      if (ms != -INFINITY) o += __ldcg(part + s * (HD + 2) + d) * exp_for<T>(ms - m);
+    }
+    dst[d] = from_f32<T>(o / total);
+  }
+}
+
+// One CTA = one (split, head, row).  Its four warps walk the split's keys in chunks of 32, each warp
+// with a running maximum, sum and output of its own, and meet once at the end: no block-wide barrier
+// stands inside the walk, so every lane has 16-byte loads of a whole chunk in flight.  Scoring: a lane
+// per key.  Values: HD/8 lanes per key, 8 dimensions each, the key's weight handed round by shuffle.
+//
+// k_new / v_new (optional): this step's keys and values of the rows, [row, kv_head * HD], as the
+// projection left them.  The key at the row's own position is then read from there, not from the
+// cache, and the CTAs of split 0 write it to the cache - the step needs no separate store kernel.
+// counters (optional, one int per (row, head), zero before the first launch): the CTA that finishes
+// last merges the splits itself and puts the counter back to zero; without counters a second kernel merges.
 template <typename T, int HD>
 __global__ void __launch_bounds__(DEC_THREADS)
 attention_decode_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict__ out, int64_t ld_out,
                         const int* __restrict__ row_seq, const int* __restrict__ row_pos,
                         const int* __restrict__ page_table, int table_width,
-                        const T* __restrict__ k_pages, const T* __restrict__ v_pages, float* __restrict__ scratch,
+                        T* __restrict__ k_pages, T* __restrict__ v_pages,
+                        const T* __restrict__ k_new, const T* __restrict__ v_new, int64_t ld_new,
+                        float* __restrict__ scratch, int* __restrict__ counters,
                         int n_heads, int n_kv_heads, int page_size, int n_splits, float scale, int window) {
-  constexpr int CH = HD / 8;                    // chunks of 8 dimensions per row
-  constexpr int KG = DEC_THREADS / CH;          // groups of keys that accumulate values side by side
-  __shared__ float qs[HD];
-  __shared__ float ps[DEC_THREADS];
-  __shared__ float red[DEC_WARPS + 1];
-  __shared__ __align__(16) float acc_sh[KG * HD];
+  constexpr int CH = HD / 8;                    // lanes that share one value row (8 dimensions each)
+  constexpr int RPI = 32 / CH;                  // value rows a warp takes per pass
+  constexpr int PASSES = (32 + RPI - 1) / RPI;
+  __shared__ __align__(16) float qs[HD];
+  __shared__ __align__(16) float acc_sh[DEC_WARPS][RPI][HD];
+  __shared__ float ml_sh[DEC_WARPS][2];
+  __shared__ int last_flag;
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int split = blockIdx.x, h = blockIdx.y, r = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int kvh = h / (n_heads / n_kv_heads);
+  const int group = n_heads / n_kv_heads;
+  const int kvh = h / group;
   const int pos = row_pos[r];
   const int* pages = page_table + (int64_t)row_seq[r] * table_width;
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
@@ -78,23 +117,40 @@ attention_decode_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict__ o
   per = (per + 63) / 64 * 64;
   const int t_begin = lo + split * per;
   const int t_end = (t_begin + per < pos + 1) ? t_begin + per : pos + 1;
+  const T* k_row_new = k_new ? k_new + (int64_t)r * ld_new + (int64_t)kvh * HD : nullptr;
+  const T* v_row_new = v_new ? v_new + (int64_t)r * ld_new + (int64_t)kvh * HD : nullptr;
 
   for (int d = tid; d < HD; d += DEC_THREADS) qs[d] = to_f32(q[(int64_t)r * ld_q + (int64_t)h * HD + d]);
+  if (k_row_new != nullptr && split == 0 && h % group == 0 && tid < 2 * CH) {
+    // this step's key and value go to their place in the cache (nobody reads that place in this launch)
+    const int page = pages[pos / page_size];
+    const int64_t dst = (((int64_t)page * n_kv_heads + kvh) * page_size + pos % page_size) * HD;
+    const int c = tid % CH;
+    const T* src = (tid < CH ? k_row_new : v_row_new) + c * 8;
+    T* to = (tid < CH ? k_pages : v_pages) + dst + c * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) to[i] = src[i];
+  }
   __syncthreads();
 
-  const int c = tid % CH, kg = tid / CH;        // this thread's slice of the value accumulation
+  const int vrow = lane / CH, vc = lane % CH;   // this lane's place in the value passes
   float acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
   float run_max = -INFINITY, run_sum = 0.f;
 
-  for (int t0 = t_begin; t0 < t_end; t0 += DEC_THREADS) {
-    // ---- one key per thread: score
-    const int t = t0 + tid;
+  for (int t0 = t_begin + warp * 32; t0 < t_end; t0 += DEC_WARPS * 32) {
+    // ---- a key per lane: score
+    const int t = t0 + lane;
     float s = -INFINITY;
     if (t < t_end) {
-      const int page = pages[t / page_size];
-      const T* kr = k_pages + (((int64_t)page * n_kv_heads + kvh) * page_size + t % page_size) * HD;
+      const T* kr;
+      if (k_row_new != nullptr && t == pos) {
+        kr = k_row_new;
+      } else {
+        const int page = pages[t / page_size];
+        kr = k_pages + (((int64_t)page * n_kv_heads + kvh) * page_size + t % page_size) * HD;
+      }
       float dot = 0.f;
 #pragma unroll
       for (int j = 0; j < CH; ++j) {
@@ -105,109 +161,118 @@ attention_decode_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict__ o
       }
       s = dot * scale;
     }
-    // ---- the tile's maximum, folded into the running one
-    float m = warp_max(s);
-    if (lane == 0) red[warp] = m;
-    __syncthreads();
-    if (tid == 0) {
-      float mm = red[0];
-#pragma unroll
-      for (int w = 1; w < DEC_WARPS; ++w) mm = fmaxf(mm, red[w]);
-      red[DEC_WARPS] = mm;
-    }
-    __syncthreads();
-    const float new_max = fmaxf(run_max, red[DEC_WARPS]);
+    const float new_max = fmaxf(run_max, warp_max(s));          // the chunk has at least one key
     const float keep = (run_max == -INFINITY) ? 0.f : exp_for<T>(run_max - new_max);
     const float p = (t < t_end) ? exp_for<T>(s - new_max) : 0.f;
-    ps[tid] = p;
-    float sum = warp_sum(p);
-    __syncthreads();                       // everyone has read red[DEC_WARPS]; ps is complete
-    if (lane == 0) red[warp] = sum;
-    __syncthreads();
-    float tile_sum = 0.f;
-#pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w) tile_sum += red[w];
-    run_sum = run_sum * keep + tile_sum;
+    run_sum = run_sum * keep + warp_sum(p);
     run_max = new_max;
-
-    // ---- values: thread (kg, c) adds keys kg, kg + KG, ... of the tile into 8 dimensions
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] *= keep;
-    const int n_here = (t_end - t0) < DEC_THREADS ? (t_end - t0) : DEC_THREADS;
-    if (kg < KG) {
-#pragma unroll 4
-      for (int j = kg; j < n_here; j += KG) {
-        const int tj = t0 + j;
-        const int page = pages[tj / page_size];
-        const T* vr = v_pages + (((int64_t)page * n_kv_heads + kvh) * page_size + tj % page_size) * HD + c * 8;
+
+    // ---- values: CH lanes per key, RPI keys per pass
+#pragma unroll
+    for (int pass = 0; pass < PASSES; ++pass) {
+      const int key = pass * RPI + vrow;                         // within the chunk
+      const float w = __shfl_sync(0xffffffffu, p, key < 32 ? key : 0);
+      const int tj = t0 + key;
+      if (vrow < RPI && key < 32 && tj < t_end) {
+        const T* vr;
+        if (v_row_new != nullptr && tj == pos) {
+          vr = v_row_new + vc * 8;
+        } else {
+          const int page = pages[tj / page_size];
+          vr = v_pages + (((int64_t)page * n_kv_heads + kvh) * page_size + tj % page_size) * HD + vc * 8;
+        }
         float f[8];
         Vec8<T>::load(vr, f);
-        const float w = ps[j];
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = fmaf(w, f[i], acc[i]);
       }
     }
-    __syncthreads();                       // ps and red are rewritten by the next tile
   }
 
-  // ---- sum the key groups, then write the result or the partial
-  if (kg < KG) {
+  // ---- the warps meet
+  if (vrow < RPI) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc_sh[kg * HD + c * 8 + i] = acc[i];
+    for (int i = 0; i < 8; ++i) acc_sh[warp][vrow][vc * 8 + i] = acc[i];
+  }
+  if (lane == 0) {
+    ml_sh[warp][0] = run_max;
+    ml_sh[warp][1] = run_sum;
   }
   __syncthreads();
+  float m = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < DEC_WARPS; ++w) m = fmaxf(m, ml_sh[w][0]);
+  float total = 0.f, wscale[DEC_WARPS];
+#pragma unroll
+  for (int w = 0; w < DEC_WARPS; ++w) {
+    wscale[w] = (ml_sh[w][0] == -INFINITY) ? 0.f : exp_for<T>(ml_sh[w][0] - m);
+    total += ml_sh[w][1] * wscale[w];
+  }
+  float* part = n_splits > 1 ? scratch + (((int64_t)r * n_heads + h) * n_splits + split) * (HD + 2) : nullptr;
   for (int d = tid; d < HD; d += DEC_THREADS) {
     float o = 0.f;
 #pragma unroll
-    for (int g = 0; g < KG; ++g) o += acc_sh[g * HD + d];
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      float ow = 0.f;
+#pragma unroll
+      for (int g = 0; g < RPI; ++g) ow += acc_sh[w][g][d];
+      o += ow * wscale[w];
+    }
     if (n_splits == 1) {
-      out[(int64_t)r * ld_out + (int64_t)h * HD + d] = from_f32<T>(o / run_sum);
+      out[(int64_t)r * ld_out + (int64_t)h * HD + d] = from_f32<T>(o / total);
     } else {
-      float* part = scratch + (((int64_t)r * n_heads + h) * n_splits + split) * (HD + 2);
       part[d] = o;
-      if (d == 0) {
-        part[HD] = run_max;
-        part[HD + 1] = run_sum;
+    }
+  }
+  if (n_splits > 1) {
+    if (tid == 0) {
+      part[HD] = m;
+      part[HD + 1] = total;
+    }
+    if (counters != nullptr) {
+      __threadfence();
+      __syncthreads();
+      if (tid == 0) {
+        const int done = atomicAdd(&counters[r * n_heads + h], 1);
+        last_flag = (done == n_splits - 1);
+        if (last_flag) counters[r * n_heads + h] = 0;            // ready for the next launch
+      }
+      __syncthreads();
+      if (last_flag) {
+        __threadfence();
+        merge_partials<T, HD>(scratch + ((int64_t)r * n_heads + h) * n_splits * (HD + 2),
+                              out + (int64_t)r * ld_out + (int64_t)h * HD, n_splits, tid, DEC_THREADS);
       }
     }
   }
 }
 
-// Merges the partial results of the splits of one (row, head).
+// The merge as a kernel of its own (when no counters are given).
 template <typename T, int HD>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ scratch, T* __restrict__ out, int64_t ld_out,
                                               int n_heads, int n_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x, h = blockIdx.y;
-  const float* part = scratch + ((int64_t)r * n_heads + h) * n_splits * (HD + 2);
-  float m = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part[s * (HD + 2) + HD]);
-  float total = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float ms = part[s * (HD + 2) + HD];
-    if (ms != -INFINITY) total += part[s * (HD + 2) + HD + 1] * exp_for<T>(ms - m);
-  }
-  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-    float o = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float ms = part[s * (HD + 2) + HD];
-      if (ms != -INFINITY) o += part[s * (HD + 2) + d] * exp_for<T>(ms - m);
-    }
-    out[(int64_t)r * ld_out + (int64_t)h * HD + d] = from_f32<T>(o / total);
-  }
+  merge_partials<T, HD>(scratch + ((int64_t)r * n_heads + h) * n_splits * (HD + 2),
+                        out + (int64_t)r * ld_out + (int64_t)h * HD, n_splits, threadIdx.x, blockDim.x);
 }
 
 template <typename T, int HD>
 int launch(const void* q, int64_t ld_q, void* out, int64_t ld_out, const int* row_seq, const int* row_pos,
-           const int* page_table, int table_width, const void* k_pages, const void* v_pages, float* scratch,
-           int n_rows, int n_heads, int n_kv_heads, int page_size, int n_splits, float scale, int window,
-           cudaStream_t stream) {
+           const int* page_table, int table_width, const void* k_pages, const void* v_pages, const void* k_new,
+           const void* v_new, int64_t ld_new, float* scratch, int* counters, int n_rows, int n_heads, int n_kv_heads,
+           int page_size, int n_splits, float scale, int window, cudaStream_t stream) {
   dim3 grid(n_splits, n_heads, n_rows);
-  attention_decode_kernel<T, HD><<<grid, DEC_THREADS, 0, stream>>>(
-      (const T*)q, ld_q, (T*)out, ld_out, row_seq, row_pos, page_table, table_width, (const T*)k_pages,
-      (const T*)v_pages, scratch, n_heads, n_kv_heads, page_size, n_splits, scale, window);
+  kvad_launch(attention_decode_kernel<T, HD>, grid, dim3(DEC_THREADS), 0, stream,
+      (const T*)q, ld_q, (T*)out, ld_out, row_seq, row_pos, page_table, table_width, (T*)const_cast<void*>(k_pages),
+      (T*)const_cast<void*>(v_pages), (const T*)k_new, (const T*)v_new, ld_new, scratch, counters, n_heads, n_kv_heads,
+      page_size, n_splits, scale, window);
   KVAD_CHECK_LAUNCH("attention_decode");
-  if (n_splits > 1) {
-    attention_decode_merge_kernel<T, HD><<<dim3(n_rows, n_heads), HD < 64 ? 32 : 64, 0, stream>>>(scratch, (T*)out, ld_out, n_heads, n_splits);
+  if (n_splits > 1 && counters == nullptr) {
+    kvad_launch(attention_decode_merge_kernel<T, HD>, dim3(n_rows, n_heads), dim3(HD < 64 ? 32 : 64), 0, stream, (const float*)scratch, (T*)out, ld_out, n_heads, n_splits);
     KVAD_CHECK_LAUNCH("attention_decode_merge");
   }
   return KVAD_OK;
@@ -220,28 +285,35 @@ KVAD_EXPORT int64_t kvad_attention_decode_scratch(int n_rows, int n_heads, int h
   return n_splits > 1 ? (int64_t)n_rows * n_heads * n_splits * (head_dim + 2) : 0;
 }
 
-KVAD_EXPORT int kvad_attention_decode(int dtype, const void* q, int64_t ld_q, void* out, int64_t ld_out,
-                                      const int* row_seq, const int* row_pos, const int* page_table, int table_width,
-                                      const void* k_pages, const void* v_pages, float* scratch, int n_rows, int n_heads,
-                                      int n_kv_heads, int head_dim, int page_size, int n_splits, float scale, int window,
-                                      cudaStream_t stream) {
+// The full form.  k_new / v_new / ld_new: this step's keys and values of the rows (or null: every key
+// is read from the cache, which then must already hold the rows' own positions).  counters: one
+// zeroed int per (row, head), left zeroed (or null: a second kernel merges the splits).
+KVAD_EXPORT int kvad_attention_decode_step(int dtype, const void* q, int64_t ld_q, void* out, int64_t ld_out,
+                                           const int* row_seq, const int* row_pos, const int* page_table,
+                                           int table_width, void* k_pages, void* v_pages, const void* k_new,
+                                           const void* v_new, int64_t ld_new, float* scratch, int* counters, int n_rows,
+                                           int n_heads, int n_kv_heads, int head_dim, int page_size, int n_splits,
+                                           float scale, int window, cudaStream_t stream) {
   KVAD_REQUIRE(n_rows >= 0 && n_heads > 0 && n_kv_heads > 0 && page_size > 0 && table_width > 0 && n_splits > 0,
                "attention_decode: bad sizes rows=%d heads=%d kv_heads=%d page=%d splits=%d", n_rows, n_heads, n_kv_heads, page_size, n_splits);
   KVAD_REQUIRE(n_heads % n_kv_heads == 0, "attention_decode: %d heads do not divide into %d key/value heads", n_heads, n_kv_heads);
   KVAD_REQUIRE(n_heads <= 65535 && n_rows <= 65535, "attention_decode: %d heads x %d rows are more than one launch takes", n_heads, n_rows);
   KVAD_REQUIRE(n_splits == 1 || scratch != nullptr, "attention_decode: %d splits need scratch memory", n_splits);
-  KVAD_REQUIRE((ld_q % 8 == 0) && ((reinterpret_cast<uintptr_t>(k_pages) & 15) == 0) && ((reinterpret_cast<uintptr_t>(v_pages) & 15) == 0),
-               "attention_decode: the cache must start on a 16-byte boundary");
+  KVAD_REQUIRE((k_new == nullptr) == (v_new == nullptr), "attention_decode: new keys and new values come together");
+  KVAD_REQUIRE((ld_q % 8 == 0) && ((reinterpret_cast<uintptr_t>(k_pages) & 15) == 0) && ((reinterpret_cast<uintptr_t>(v_pages) & 15) == 0) &&
+                   (k_new == nullptr || (ld_new % 8 == 0 && (reinterpret_cast<uintptr_t>(k_new) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_new) & 15) == 0)),
+               "attention_decode: queries, new keys/values and the cache must be 16-byte aligned with row strides that are multiples of 8");
   if (n_rows == 0) return KVAD_OK;
 #define KVAD_DEC_CASE(HD)                                                                                              \
   case HD:                                                                                                             \
     if (dtype == KVAD_DTYPE_BF16)                                                                                      \
       return launch<__nv_bfloat16, HD>(q, ld_q, out, ld_out, row_seq, row_pos, page_table, table_width, k_pages,       \
-                                       v_pages, scratch, n_rows, n_heads, n_kv_heads, page_size, n_splits, scale,      \
-                                       window, stream);                                                                \
+                                       v_pages, k_new, v_new, ld_new, scratch, counters, n_rows, n_heads, n_kv_heads,  \
+                                       page_size, n_splits, scale, window, stream);                                    \
     if (dtype == KVAD_DTYPE_F32)                                                                                       \
       return launch<float, HD>(q, ld_q, out, ld_out, row_seq, row_pos, page_table, table_width, k_pages, v_pages,      \
-                               scratch, n_rows, n_heads, n_kv_heads, page_size, n_splits, scale, window, stream);      \
+                               k_new, v_new, ld_new, scratch, counters, n_rows, n_heads, n_kv_heads, page_size,        \
+                               n_splits, scale, window, stream);                                                       \
     break;
   switch (head_dim) {
     KVAD_DEC_CASE(16) KVAD_DEC_CASE(32) KVAD_DEC_CASE(48) KVAD_DEC_CASE(64) KVAD_DEC_CASE(80) KVAD_DEC_CASE(96)
@@ -251,6 +323,18 @@ KVAD_EXPORT int kvad_attention_decode(int dtype, const void* q, int64_t ld_q, vo
   }
 #undef KVAD_DEC_CASE
   KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention_decode: unknown dtype %d", dtype);
+}
+
+// The cache already holds every position; a second kernel merges the splits.
+KVAD_EXPORT int kvad_attention_decode(int dtype, const void* q, int64_t ld_q, void* out, int64_t ld_out,
+                                      const int* row_seq, const int* row_pos, const int* page_table, int table_width,
+                                      const void* k_pages, const void* v_pages, float* scratch, int n_rows, int n_heads,
+                                      int n_kv_heads, int head_dim, int page_size, int n_splits, float scale, int window,
+                                      cudaStream_t stream) {
+  return kvad_attention_decode_step(dtype, q, ld_q, out, ld_out, row_seq, row_pos, page_table, table_width,
+                                    const_cast<void*>(k_pages), const_cast<void*>(v_pages), nullptr, nullptr, 0, scratch,
+                                    nullptr, n_rows, n_heads, n_kv_heads, head_dim, page_size, n_splits, scale, window,
+                                    stream);
 }
 
 // ---------------------------------------------------------------------------------------------

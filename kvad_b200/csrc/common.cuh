@@ -39,10 +39,38 @@ static thread_local char kvad_err_text[768];
       KVAD_FAIL(KVAD_ERR_CUDA, "%s: launch failed: %s", what, cudaGetErrorString(e__)); \
   } while (0)
 
-#define KVAD_DEFINE_LAST_ERROR()                                  \
-  KVAD_EXPORT const char* kvad_last_error() { return kvad_err_text; }
+// Programmatic dependent launch: with it on, a kernel is launched so that it may start while the
+// kernel before it in the stream is still running; it does what does not depend on that kernel
+// (set-up, fetching weights) and then waits (pdl_wait) before it touches anything the stream's
+// earlier work produced.  Every kernel of this library writes global memory only after pdl_wait.
+static int kvad_pdl_enabled = 0;
+
+#define KVAD_DEFINE_LAST_ERROR()                                                  \
+  KVAD_EXPORT const char* kvad_last_error() { return kvad_err_text; }             \
+  KVAD_EXPORT void kvad_set_pdl(int on) { kvad_pdl_enabled = on ? 1 : 0; }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t kvad_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                      cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = kvad_pdl_enabled ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 namespace kvad {
+
+// Waits until everything earlier in the stream has completed and is visible (a no-op unless the
+// kernel was launched as a programmatic dependent); lets the next kernel in the stream start.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }

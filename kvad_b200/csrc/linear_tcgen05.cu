@@ -237,9 +237,19 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  pdl_launch_dependents();
   if (warp == 0) {
     if (lane == 0) {
-      for (int i = 0; i < num_kb; ++i) {
+      // weights do not depend on the kernel before: their first stages are on the way before the wait
+      const int pre = num_kb < STAGES ? num_kb : STAGES;
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(&full_bar[i], T::A_BYTES + T::B_BYTES);
+        tma_load_2d(b_tiles + i * T::B_BYTES, &map_w, &full_bar[i], (kb_begin + i) * BK, n0);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(a_tiles + i * T::A_BYTES, &map_a, &full_bar[i], (kb_begin + i) * BK, m0);
+      for (int i = pre; i < num_kb; ++i) {
         const int s = i % STAGES;
         const uint32_t phase = (i / STAGES) & 1;
         if (!mbar_wait(&empty_bar[s], phase ^ 1)) break;
@@ -272,6 +282,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   } else {
     const int quarter = warp & 3;       // the 32 tensor-memory lanes this warp may read
     const int row = m0 + quarter * 32 + lane;
+    pdl_wait();
     const bool ok = mbar_wait(tmem_full_bar, 0);
     tc_fence_after();
     if (ok) {
@@ -349,9 +360,19 @@ linear_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  pdl_launch_dependents();
   if (warp == 0) {
     if (lane == 0) {
-      for (int i = 0; i < num_kb; ++i) {
+      // this CTA's weights (often all of them) are requested before the kernel before has finished
+      const int pre = num_kb < STAGES ? num_kb : STAGES;
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(&full_bar[i], T::W_BYTES + T::A_BYTES);
+        tma_load_2d(w_tiles + i * T::W_BYTES, &map_w, &full_bar[i], (kb_begin + i) * BK, n0);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(a_tiles + i * T::A_BYTES, &map_a, &full_bar[i], (kb_begin + i) * BK, 0);
+      for (int i = pre; i < num_kb; ++i) {
         const int s = i % STAGES;
         const uint32_t phase = (i / STAGES) & 1;
         if (!mbar_wait(&empty_bar[s], phase ^ 1)) break;
@@ -380,6 +401,7 @@ linear_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __
   } else {
     const int quarter = warp & 3;
     const int n = n0 + quarter * 32 + lane;
+    pdl_wait();
     const bool ok = mbar_wait(tmem_full_bar, 0);
     tc_fence_after();
     if (ok) {
@@ -504,7 +526,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, const void* bias, int b
   const int kb_per_split = (kb_total + splits - 1) / splits;
   const int z = (kb_total + kb_per_split - 1) / kb_per_split;
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, z);
-  linear_tcgen05_kernel<BN, EPI><<<grid, NUM_THREADS, T::SMEM, stream>>>(ma, mw, bias, bias_f32, out, ldo, M, N, K, kb_per_split);
+  kvad_launch(linear_tcgen05_kernel<BN, EPI>, grid, dim3(NUM_THREADS), T::SMEM, stream, ma, mw, bias, bias_f32, out, ldo, M, N, K, kb_per_split);
   KVAD_CHECK_LAUNCH("linear_tcgen05");
   return KVAD_OK;
 }
@@ -536,7 +558,7 @@ int launch_skinny(const CUtensorMap& ma, const CUtensorMap& mw, const void* bias
   const int kb_per_split = (kb_total + splits - 1) / splits;
   const int z = (kb_total + kb_per_split - 1) / kb_per_split;
   dim3 grid((N + BM - 1) / BM, z);
-  linear_tcgen05_skinny_kernel<MB, EPI><<<grid, NUM_THREADS, T::SMEM, stream>>>(ma, mw, bias, bias_f32, out, ldo, M, N, K, kb_per_split);
+  kvad_launch(linear_tcgen05_skinny_kernel<MB, EPI>, grid, dim3(NUM_THREADS), T::SMEM, stream, ma, mw, bias, bias_f32, out, ldo, M, N, K, kb_per_split);
   KVAD_CHECK_LAUNCH("linear_tcgen05_skinny");
   return KVAD_OK;
 }

@@ -13,6 +13,8 @@ template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
                              const T* __restrict__ wte, const T* __restrict__ wpe,
                              float* __restrict__ x, int n_rows, int width, int vocab, int n_positions) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t total = (int64_t)n_rows * width;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
@@ -39,9 +41,9 @@ KVAD_EXPORT int kvad_embed(int dtype, const int* tokens, const int* positions, c
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == KVAD_DTYPE_F32)
-    embed_kernel<float><<<blocks, threads, 0, stream>>>(tokens, positions, (const float*)wte, (const float*)wpe, x, n_rows, width, vocab, n_positions);
+    kvad_launch(embed_kernel<float>, dim3(blocks), dim3(threads), 0, stream, tokens, positions, (const float*)wte, (const float*)wpe, x, n_rows, width, vocab, n_positions);
   else if (dtype == KVAD_DTYPE_BF16)
-    embed_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(tokens, positions, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, x, n_rows, width, vocab, n_positions);
+    kvad_launch(embed_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, tokens, positions, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, x, n_rows, width, vocab, n_positions);
   else
     KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "embed: unknown dtype %d", dtype);
   KVAD_CHECK_LAUNCH("embed");
@@ -62,6 +64,8 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
                                  int params_f32, T* __restrict__ out, int width, float eps) {
   extern __shared__ float row[];
   __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const int64_t src = row_index ? (int64_t)row_index[r] : (int64_t)r;
   const float* xr = x + src * width;
@@ -98,10 +102,10 @@ KVAD_EXPORT int kvad_layernorm(int out_dtype, const float* x, const int* row_ind
   const int threads = width >= 1024 ? 256 : 128;
   if (out_dtype == KVAD_DTYPE_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    layernorm_kernel<float><<<n_rows, threads, smem, stream>>>(x, row_index, gain, bias, params_f32, (float*)out, width, eps);
+    kvad_launch(layernorm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, x, row_index, gain, bias, params_f32, (float*)out, width, eps);
   } else if (out_dtype == KVAD_DTYPE_BF16) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    layernorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, stream>>>(x, row_index, gain, bias, params_f32, (__nv_bfloat16*)out, width, eps);
+    kvad_launch(layernorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, stream, x, row_index, gain, bias, params_f32, (__nv_bfloat16*)out, width, eps);
   } else {
     KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "layernorm: unknown dtype %d", out_dtype);
   }
@@ -122,6 +126,8 @@ __global__ void kv_store_kernel(const T* __restrict__ k_src, const T* __restrict
                                 const int* __restrict__ page_table, int table_width,
                                 T* __restrict__ k_pages, T* __restrict__ v_pages,
                                 int n_rows, int n_kv_heads, int head_dim, int page_size) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int kv_width = n_kv_heads * head_dim;
   const int64_t total = (int64_t)n_rows * kv_width;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -147,9 +153,9 @@ KVAD_EXPORT int kvad_kv_store(int dtype, const void* k_src, const void* v_src, i
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == KVAD_DTYPE_F32)
-    kv_store_kernel<float><<<blocks, threads, 0, stream>>>((const float*)k_src, (const float*)v_src, ld_src, row_seq, row_pos, page_table, table_width, (float*)k_pages, (float*)v_pages, n_rows, n_kv_heads, head_dim, page_size);
+    kvad_launch(kv_store_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)k_src, (const float*)v_src, ld_src, row_seq, row_pos, page_table, table_width, (float*)k_pages, (float*)v_pages, n_rows, n_kv_heads, head_dim, page_size);
   else if (dtype == KVAD_DTYPE_BF16)
-    kv_store_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)k_src, (const __nv_bfloat16*)v_src, ld_src, row_seq, row_pos, page_table, table_width, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, n_rows, n_kv_heads, head_dim, page_size);
+    kvad_launch(kv_store_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)k_src, (const __nv_bfloat16*)v_src, ld_src, row_seq, row_pos, page_table, table_width, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, n_rows, n_kv_heads, head_dim, page_size);
   else
     KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "kv_store: unknown dtype %d", dtype);
   KVAD_CHECK_LAUNCH("kv_store");

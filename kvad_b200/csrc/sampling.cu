@@ -178,6 +178,8 @@ sample_kernel(const float* __restrict__ logits, int64_t ld, int vocab,
               int* __restrict__ out) {
   extern __shared__ unsigned char raw[];
   Shared& sh = *reinterpret_cast<Shared*>(raw);
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x, tid = threadIdx.x;
   const float* row = logits + (int64_t)r * ld;
   const float temp = temperature[r];
@@ -265,7 +267,7 @@ KVAD_EXPORT int kvad_sample(const float* logits, int64_t ld, int n_rows, int voc
     if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "sample: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  sample_kernel<<<n_rows, SAMPLE_THREADS, smem, stream>>>(logits, ld, vocab, temperature, top_k, top_p, uniform, out);
+  kvad_launch(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), smem, stream, logits, ld, vocab, temperature, top_k, top_p, uniform, out);
   KVAD_CHECK_LAUNCH("sample");
   return KVAD_OK;
 }
@@ -275,6 +277,8 @@ __global__ void __launch_bounds__(256)
 argmax_kernel(const float* __restrict__ logits, int64_t ld, int vocab, int* __restrict__ out) {
   __shared__ float scratch[33];
   __shared__ int winner;
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x, tid = threadIdx.x;
   const float* row = logits + (int64_t)r * ld;
   float best = -INFINITY;
@@ -300,6 +304,8 @@ __global__ void __launch_bounds__(256)
 argmax_partial_kernel(const float* __restrict__ logits, int64_t ld, int vocab, unsigned long long* __restrict__ partial,
                       int n_chunks) {
   __shared__ unsigned long long keys[8];
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.y, chunk = blockIdx.x, tid = threadIdx.x;
   const float* row = logits + (int64_t)r * ld;
   const int begin = chunk * ARGMAX_CHUNK;
@@ -324,6 +330,8 @@ argmax_partial_kernel(const float* __restrict__ logits, int64_t ld, int vocab, u
 
 __global__ void __launch_bounds__(32)
 argmax_final_kernel(const unsigned long long* __restrict__ partial, int n_chunks, int* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   unsigned long long best = 0ull;
   for (int i = threadIdx.x; i < n_chunks; i += 32) {
@@ -350,15 +358,15 @@ KVAD_EXPORT int kvad_argmax(const float* logits, int64_t ld, int n_rows, int voc
   KVAD_REQUIRE(n_rows >= 0 && vocab > 0 && ld >= vocab, "argmax: bad sizes rows=%d vocab=%d ld=%lld", n_rows, vocab, (long long)ld);
   if (n_rows == 0) return KVAD_OK;
   if (scratch == nullptr) {
-    argmax_kernel<<<n_rows, 256, 0, stream>>>(logits, ld, vocab, out);
+    kvad_launch(argmax_kernel, dim3(n_rows), dim3(256), 0, stream, logits, ld, vocab, out);
     KVAD_CHECK_LAUNCH("argmax");
     return KVAD_OK;
   }
   KVAD_REQUIRE(n_rows <= 65535, "argmax: %d rows are more than one launch takes", n_rows);
   const int n_chunks = (vocab + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
-  argmax_partial_kernel<<<dim3(n_chunks, n_rows), 256, 0, stream>>>(logits, ld, vocab, scratch, n_chunks);
+  kvad_launch(argmax_partial_kernel, dim3(n_chunks, n_rows), dim3(256), 0, stream, logits, ld, vocab, scratch, n_chunks);
   KVAD_CHECK_LAUNCH("argmax_partial");
-  argmax_final_kernel<<<n_rows, 32, 0, stream>>>(scratch, n_chunks, out);
+  kvad_launch(argmax_final_kernel, dim3(n_rows), dim3(32), 0, stream, (const unsigned long long*)scratch, n_chunks, out);
   KVAD_CHECK_LAUNCH("argmax_final");
   return KVAD_OK;
 }

@@ -10,6 +10,7 @@ computes anything here, and nothing falls back to the CPU.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_int64, c_void_p
 from typing import Optional
 
@@ -62,9 +63,9 @@ _SIGNATURES = {
                                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     },
     "attention_decode": {
-        "kvad_attention_decode": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
-                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                                  c_void_p],
+        "kvad_attention_decode_step": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
+                                       c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
+                                       c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     },
     "sampling": {
         "kvad_sample": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -73,6 +74,17 @@ _SIGNATURES = {
 }
 
 _bound: dict[str, ctypes.CDLL] = {}
+_pdl = os.environ.get("KVAD_PDL", "1") != "0"
+
+
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch for every kernel of the library: a kernel may start (set up,
+    fetch its weights) while the one before it in the stream still runs.  On by default; KVAD_PDL=0
+    or set_pdl(False) launches plainly."""
+    global _pdl
+    _pdl = bool(on)
+    for handle in _bound.values():
+        handle.kvad_set_pdl(int(_pdl))
 
 
 def lib(name: str) -> ctypes.CDLL:
@@ -85,6 +97,9 @@ def lib(name: str) -> ctypes.CDLL:
         f = getattr(handle, fn)
         f.argtypes = argtypes
         f.restype = c_int
+    handle.kvad_set_pdl.argtypes = [c_int]
+    handle.kvad_set_pdl.restype = None
+    handle.kvad_set_pdl(int(_pdl))
     _bound[name] = handle
     return handle
 
@@ -140,6 +155,7 @@ class Ops:
         self.tensor_core_linear = dtype == torch.bfloat16 and "linear_tcgen05" in build.sources()
         self.tensor_core_prefill = dtype == torch.bfloat16 and "attention_prefill" in build.sources()
         self.fast_decode = dtype == torch.bfloat16 and "attention_decode" in build.sources()
+        self._counters = None       # zeroed ints the decode kernel counts finished splits in (left zeroed by it)
 
     # -- embedding -----------------------------------------------------------------
     def embed(self, tokens, positions, wte, wpe, out) -> None:
@@ -280,10 +296,15 @@ class Ops:
         return max(1, min(want, table_width, 32))
 
     def attention_decode(self, q, out, row_seq, row_pos, page_table, k_pages, v_pages, n_heads: int, scale: float,
-                         window: int = 0, *, n_splits: int = 1, scratch=None) -> None:
-        """Single-token rows over the cache, keys split over CTAs (decode kernel).  `scratch`: float32,
-        `n_rows * n_heads * n_splits * (head_dim + 2)` elements when `n_splits > 1`."""
-        _need_cuda(q, out, row_seq, row_pos, page_table, k_pages, v_pages, scratch)
+                         window: int = 0, *, n_splits: int = 1, scratch=None, k_new=None, v_new=None,
+                         merge_in_kernel: bool = False) -> None:
+        """Single-token rows over the cache, keys split over CTAs (decode kernel).
+
+        `scratch`: float32, `n_rows * n_heads * n_splits * (head_dim + 2)` elements when `n_splits > 1`.
+        `k_new` / `v_new`: this step's keys and values of the rows (views `[rows, kv_heads * head_dim]` of
+        one buffer); given, the kernel reads each row's own position from them and writes it to the
+        cache itself.  `merge_in_kernel`: the CTA that finishes last merges the splits (else a second kernel)."""
+        _need_cuda(q, out, row_seq, row_pos, page_table, k_pages, v_pages, scratch, k_new, v_new)
         ld_q, ld_o = _rows_view(q, "attention queries"), _rows_view(out, "attention output")
         _, n_kv, page, hd = k_pages.shape
         n = q.shape[0]
@@ -294,12 +315,23 @@ class Ops:
         if n_splits > 1 and (scratch is None or scratch.dtype != torch.float32
                              or scratch.numel() < n * n_heads * n_splits * (hd + 2)):
             raise KernelError("attention_decode: scratch must be float32 with rows x heads x splits x (head_dim + 2) elements")
+        ld_new = 0
+        if k_new is not None:
+            ld_new = _rows_view(k_new, "new keys")
+            if (v_new is None or _rows_view(v_new, "new values") != ld_new or k_new.shape != (n, n_kv * hd)
+                    or v_new.shape != k_new.shape or k_new.dtype != self.dtype or v_new.dtype != self.dtype):
+                raise KernelError("attention_decode: new keys and values must be views [rows, kv_heads x head size] of one buffer")
+        counters = None
+        if merge_in_kernel and n_splits > 1:
+            if self._counters is None or self._counters.numel() < n * n_heads:
+                self._counters = torch.zeros(max(4096, n * n_heads), dtype=torch.int32, device=q.device)
+            counters = self._counters
         h = lib("attention_decode")
-        _check(h.kvad_attention_decode(self.code, _ptr(q), ld_q, _ptr(out), ld_o, _ptr(row_seq), _ptr(row_pos),
-                                       _ptr(page_table), page_table.shape[1], _ptr(k_pages), _ptr(v_pages),
-                                       _ptr(scratch), n, n_heads, n_kv, hd, page, int(n_splits), float(scale),
-                                       int(window or 0), _stream()), h)
-        if n_splits > 1:
+        _check(h.kvad_attention_decode_step(self.code, _ptr(q), ld_q, _ptr(out), ld_o, _ptr(row_seq), _ptr(row_pos),
+                                            _ptr(page_table), page_table.shape[1], _ptr(k_pages), _ptr(v_pages),
+                                            _ptr(k_new), _ptr(v_new), ld_new, _ptr(scratch), _ptr(counters), n, n_heads,
+                                            n_kv, hd, page, int(n_splits), float(scale), int(window or 0), _stream()), h)
+        if n_splits > 1 and counters is None:
             global _launches
             _launches += 1          # the merge kernel
 

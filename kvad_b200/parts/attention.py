@@ -58,10 +58,8 @@ class CausalSelfAttention(Mixer):
         if self.position is not None:
             self.position.rotate(ctx, q, k)
         view = ctx.kv(call.cache)
-        if call.writes_cache:
-            ctx.ops.kv_store(k, v, ctx.row_seq, ctx.row_pos, view.page_table, view.k_pages, view.v_pages)
         mixed = ctx.buffer((n, self.q_width))
-        ctx.attend(q, mixed, view, self.n_heads, self.score_scale)
+        ctx.attend(q, k, v, mixed, view, self.n_heads, self.score_scale, call.writes_cache)
         self.out.forward(ctx, mixed, residual, "residual")
 
 

@@ -214,3 +214,27 @@ def test_no_cpu_path(model_dirs):
     x = torch.zeros(2, 8)
     with pytest.raises(KernelError, match="no CPU path"):
         ops.layernorm(x, torch.ones(8), None, 1e-5, torch.zeros(2, 8))
+
+
+def test_dependent_launch_changes_no_result(engines, plains):
+    """Kernels may start before the one before them has finished (they wait before touching its output):
+    the 32-bit logits are the same bits with that switched off, and the bfloat16 ones stay right."""
+    from kvad_b200 import ops
+    t = random_tokens(950, 100, 512)
+    outs = {}
+    try:
+        for on in (True, False):
+            ops.set_pdl(on)
+            for dtype in ("float32", "bfloat16"):
+                e = engines("A", dtype)
+                s = e.open()
+                got = [e.step([StepEntry(s, t[:90], range(90))]).cpu().numpy()]
+                for j in range(90, 100):
+                    got.append(e.step([StepEntry(s, [t[j]], [0])]).cpu().numpy())
+                e.close(s)
+                outs[(on, dtype)] = np.concatenate(got)
+    finally:
+        ops.set_pdl(True)
+    assert np.array_equal(outs[(True, "float32")], outs[(False, "float32")])
+    ref = plains("A", "bfloat16").logits(t)
+    assert rel_err(outs[(True, "bfloat16")], ref) < TOL["bfloat16"] and rel_err(outs[(False, "bfloat16")], ref) < TOL["bfloat16"]

@@ -369,6 +369,27 @@ def test_attention_decode_split_keys(dtype, hd, n_heads, n_kv, window):
     with pytest.raises(KernelError, match="scratch"):
         ops.attention_decode(q_d, out, dev(row_seq), dev(row_pos), dev(table), dev(kp), dev(vp), n_heads, scale, window,
                              n_splits=3, scratch=None)
+    # the step's own key and value handed in beside the cache: their place in the cache holds NaN before the
+    # launch and the right rows after it, the result is the same, and the last CTA merges (twice: the counters
+    # it uses must come back to zero)
+    kw = n_kv * hd
+    new = torch.zeros(len(lens), 2 * kw + 8).to(DT[dtype])
+    kp2, vp2 = kp.clone(), vp.clone()
+    for s_, l in enumerate(lens):
+        new[s_, :kw], new[s_, kw:2 * kw] = ks[s_][l - 1].reshape(-1), vs[s_][l - 1].reshape(-1)
+        kp2[table[s_, (l - 1) // 64], :, (l - 1) % 64] = float("nan")
+        vp2[table[s_, (l - 1) // 64], :, (l - 1) % 64] = float("nan")
+    new_d, kp_d, vp_d = dev(new), dev(kp2), dev(vp2)
+    for splits in (1, 3, 3, 16):
+        out = torch.full((len(lens), n_heads * hd), float("nan"), device="cuda", dtype=DT[dtype])
+        scratch = torch.full((len(lens) * n_heads * splits * (hd + 2),), float("nan"), device="cuda")
+        ops.attention_decode(q_d, out, dev(row_seq), dev(row_pos), dev(table), kp_d, vp_d, n_heads, scale, window,
+                             n_splits=splits, scratch=scratch, k_new=new_d[:, :kw], v_new=new_d[:, kw:2 * kw],
+                             merge_in_kernel=True)
+        assert rel(out, ref) < KTOL[dtype], ("new", splits)
+        same = lambda a, b: torch.equal(torch.nan_to_num(a.float().cpu(), nan=7.0), torch.nan_to_num(b.float(), nan=7.0))
+        assert same(kp_d, kp) and same(vp_d, vp)
+    assert int(ops._counters.abs().sum()) == 0
 
 
 def test_attention_decode_finds_one_far_key():

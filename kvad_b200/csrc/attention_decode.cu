@@ -260,16 +260,295 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ scratch,
                         out + (int64_t)r * ld_out + (int64_t)h * HD, n_splits, threadIdx.x, blockDim.x);
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same work fed by the TMA engine (head sizes whose rows split evenly over a warp: 16, 32, 64,
+// 128, 256).  One page of one head is one contiguous tile of keys and one of values; a producer warp
+// streams them into a ring of shared-memory stages with cp.async.bulk, each stage signalling an
+// mbarrier, so that the bytes in flight do not depend on registers or on how many warps are
+// resident.  Four consumer warps take 16 keys of every tile each: HD/8 lanes per key both for the
+// score (partial dots met by shuffles) and for the value sum, so a lane keeps the weight of its own
+// key and nothing is handed round.  Pages of earlier steps do not depend on the kernel before this
+// one, so their first stages are requested before the dependent-launch wait.
+// Every wait is bounded; one that runs out raises g_decode_timeouts and the CTA runs on to its end.
+// ---------------------------------------------------------------------------------------------
+bool g_force_plain = false;      // tests: keep every head size on the kernel that loads through registers
+constexpr int TMA_CONSUMER_WARPS = 4;
+constexpr int TMA_THREADS = (TMA_CONSUMER_WARPS + 1) * 32;
+constexpr int TILE_KEYS = 64;
+constexpr uint32_t DEC_WAIT_LIMIT = 1u << 24;
+__device__ int g_decode_timeouts = 0;
+
+__device__ __forceinline__ uint32_t dec_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void dec_mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(dec_smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void dec_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(dec_smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void dec_mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(dec_smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool dec_mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < DEC_WAIT_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(dec_smem_u32(bar)), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  atomicAdd(&g_decode_timeouts, 1);
+  return false;
+}
+__device__ __forceinline__ void dec_bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dec_smem_u32(dst)), "l"(src), "r"(bytes), "r"(dec_smem_u32(bar)) : "memory");
+}
+
+template <typename T, int HD> struct DecTile {
+  static constexpr int TILE_BYTES = TILE_KEYS * HD * (int)sizeof(T);     // keys (or values) of one page and head
+  static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+  static constexpr int STAGES_RAW = 65536 / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 4 ? 4 : (STAGES_RAW < 2 ? 2 : STAGES_RAW);
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 2 * STAGES * 8 + 128;
+};
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(TMA_THREADS)
+attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict__ out, int64_t ld_out,
+                            const int* __restrict__ row_seq, const int* __restrict__ row_pos,
+                            const int* __restrict__ page_table, int table_width,
+                            T* __restrict__ k_pages, T* __restrict__ v_pages,
+                            const T* __restrict__ k_new, const T* __restrict__ v_new, int64_t ld_new,
+                            float* __restrict__ scratch, int* __restrict__ counters,
+                            int n_heads, int n_kv_heads, int n_splits, float scale, int window) {
+  using D = DecTile<T, HD>;
+  constexpr int STAGES = D::STAGES;
+  constexpr int CH = HD / 8;                       // lanes per key
+  constexpr int KPP = 32 / CH;                     // keys a warp takes per pass
+  constexpr int WARP_KEYS = TILE_KEYS / TMA_CONSUMER_WARPS;
+  constexpr int PASSES = (WARP_KEYS + KPP - 1) / KPP;
+  extern __shared__ unsigned char dec_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(dec_raw) + 127) & ~(uintptr_t)127);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(base + (size_t)STAGES * D::STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  __shared__ __align__(16) float acc_sh[TMA_CONSUMER_WARPS][HD];
+  __shared__ float ml_sh[TMA_CONSUMER_WARPS][2];
+  __shared__ int last_flag;
+
+  pdl_launch_dependents();
+  const int split = blockIdx.x, h = blockIdx.y, r = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int group = n_heads / n_kv_heads;
+  const int kvh = h / group;
+  const int pos = row_pos[r];                      // uploaded by the host before the step's first kernel
+  const int* pages = page_table + (int64_t)row_seq[r] * table_width;
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int n_keys = pos - lo + 1;
+  int per = (n_keys + n_splits - 1) / n_splits;
+  per = (per + 63) / 64 * 64;
+  const int t_begin = lo + split * per;
+  const int t_end = (t_begin + per < pos + 1) ? t_begin + per : pos + 1;
+  const int j0 = t_begin / TILE_KEYS;
+  const int n_tiles = t_end > t_begin ? (t_end - 1) / TILE_KEYS - j0 + 1 : 0;
+  const T* k_row_new = k_new ? k_new + (int64_t)r * ld_new + (int64_t)kvh * HD : nullptr;
+  const T* v_row_new = v_new ? v_new + (int64_t)r * ld_new + (int64_t)kvh * HD : nullptr;
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      dec_mbar_init(&full_bar[s], 1);
+      dec_mbar_init(&empty_bar[s], TMA_CONSUMER_WARPS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+
+  const int c = lane % CH, kl = lane / CH;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  float run_max = -INFINITY, run_sum = 0.f;
+
+  if (warp == TMA_CONSUMER_WARPS) {
+    // ---- producer
+    auto issue = [&](int i) {
+      const int s = i % STAGES;
+      const int page = pages[j0 + i];
+      const T* kt = k_pages + ((int64_t)page * n_kv_heads + kvh) * TILE_KEYS * HD;
+      const T* vt = v_pages + ((int64_t)page * n_kv_heads + kvh) * TILE_KEYS * HD;
+      unsigned char* dst = base + (size_t)s * D::STAGE_BYTES;
+      dec_mbar_expect_tx(&full_bar[s], D::STAGE_BYTES);
+      dec_bulk_load(dst, kt, D::TILE_BYTES, &full_bar[s]);
+      dec_bulk_load(dst + D::TILE_BYTES, vt, D::TILE_BYTES, &full_bar[s]);
+    };
+    // with the step's own key handed in, nothing read from the pages depends on the kernel before
+    const int pre = (k_row_new != nullptr) ? (n_tiles < STAGES ? n_tiles : STAGES) : 0;
+    if (lane == 0)
+      for (int i = 0; i < pre; ++i) issue(i);
+    pdl_wait();
+    if (k_row_new != nullptr && split == 0 && h % group == 0) {
+      // this step's key and value go to their place in the cache (no CTA of this launch reads that place)
+      const int page = pages[pos / TILE_KEYS];
+      const int64_t dst = (((int64_t)page * n_kv_heads + kvh) * TILE_KEYS + pos % TILE_KEYS) * HD;
+      for (int idx = lane; idx < 2 * CH; idx += 32) {
+        const int cc = idx % CH;
+        const T* src = (idx < CH ? k_row_new : v_row_new) + cc * 8;
+        T* to = (idx < CH ? k_pages : v_pages) + dst + cc * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) to[i] = src[i];
+      }
+    }
+    if (lane == 0) {
+      for (int i = pre; i < n_tiles; ++i) {
+        const int s = i % STAGES;
+        if (i >= STAGES && !dec_mbar_wait(&empty_bar[s], ((i / STAGES) & 1) ^ 1)) break;
+        issue(i);
+      }
+    }
+  } else {
+    // ---- consumers
+    pdl_wait();
+    float qreg[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) qreg[i] = to_f32(q[(int64_t)r * ld_q + (int64_t)h * HD + c * 8 + i]);
+    for (int i = 0; i < n_tiles; ++i) {
+      const int s = i % STAGES;
+      if (!dec_mbar_wait(&full_bar[s], (i / STAGES) & 1)) break;
+      const T* Kt = reinterpret_cast<const T*>(base + (size_t)s * D::STAGE_BYTES);
+      const T* Vt = reinterpret_cast<const T*>(base + (size_t)s * D::STAGE_BYTES + D::TILE_BYTES);
+      const int tile_key0 = (j0 + i) * TILE_KEYS;
+      float sc[PASSES];
+      float chunk_max = -INFINITY;
+#pragma unroll
+      for (int pass = 0; pass < PASSES; ++pass) {
+        const int key = warp * WARP_KEYS + pass * KPP + kl;
+        const int t = tile_key0 + key;
+        const bool valid = (pass * KPP + kl < WARP_KEYS) && t >= t_begin && t < t_end;
+        float f[8];
+        if (k_row_new != nullptr && t == pos) Vec8<T>::load(k_row_new + c * 8, f);
+        else Vec8<T>::load(Kt + key * HD + c * 8, f);
+        float dot = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dot = fmaf(qreg[e], f[e], dot);
+#pragma unroll
+        for (int o = 1; o < CH; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        sc[pass] = valid ? dot * scale : -INFINITY;
+        chunk_max = fmaxf(chunk_max, sc[pass]);
+      }
+#pragma unroll
+      for (int o = CH; o < 32; o <<= 1) chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, o));
+      const float new_max = fmaxf(run_max, chunk_max);
+      const float keep = (run_max == -INFINITY) ? 0.f : exp_for<T>(run_max - new_max);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] *= keep;
+      float chunk_sum = 0.f;
+#pragma unroll
+      for (int pass = 0; pass < PASSES; ++pass) {
+        const int key = warp * WARP_KEYS + pass * KPP + kl;
+        const int t = tile_key0 + key;
+        if (sc[pass] != -INFINITY) {                  // a key outside the range adds nothing, whatever its page holds
+          const float p = exp_for<T>(sc[pass] - new_max);
+          chunk_sum += p;
+          float f[8];
+          if (v_row_new != nullptr && t == pos) Vec8<T>::load(v_row_new + c * 8, f);
+          else Vec8<T>::load(Vt + key * HD + c * 8, f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = fmaf(p, f[e], acc[e]);
+        }
+      }
+#pragma unroll
+      for (int o = CH; o < 32; o <<= 1) chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, o);
+      run_sum = run_sum * keep + chunk_sum;
+      run_max = new_max;
+      __syncwarp();
+      if (lane == 0) dec_mbar_arrive(&empty_bar[s]);
+    }
+    // the warp's key groups meet
+#pragma unroll
+    for (int o = CH; o < 32; o <<= 1) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
+    }
+    if (kl == 0) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc_sh[warp][c * 8 + e] = acc[e];
+    }
+    if (lane == 0) {
+      ml_sh[warp][0] = run_max;
+      ml_sh[warp][1] = run_sum;
+    }
+  }
+  __syncthreads();
+
+  // ---- the warps meet
+  float m = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < TMA_CONSUMER_WARPS; ++w) m = fmaxf(m, ml_sh[w][0]);
+  float total = 0.f, wscale[TMA_CONSUMER_WARPS];
+#pragma unroll
+  for (int w = 0; w < TMA_CONSUMER_WARPS; ++w) {
+    wscale[w] = (ml_sh[w][0] == -INFINITY) ? 0.f : exp_for<T>(ml_sh[w][0] - m);
+    total += ml_sh[w][1] * wscale[w];
+  }
+  float* part = n_splits > 1 ? scratch + (((int64_t)r * n_heads + h) * n_splits + split) * (HD + 2) : nullptr;
+  for (int d = tid; d < HD; d += TMA_THREADS) {
+    float o = 0.f;
+#pragma unroll
+    for (int w = 0; w < TMA_CONSUMER_WARPS; ++w) o += acc_sh[w][d] * wscale[w];
+    if (n_splits == 1) out[(int64_t)r * ld_out + (int64_t)h * HD + d] = from_f32<T>(o / total);
+    else part[d] = o;
+  }
+  if (n_splits > 1) {
+    if (tid == 0) {
+      part[HD] = m;
+      part[HD + 1] = total;
+    }
+    if (counters != nullptr) {
+      __threadfence();
+      __syncthreads();
+      if (tid == 0) {
+        const int done = atomicAdd(&counters[r * n_heads + h], 1);
+        last_flag = (done == n_splits - 1);
+        if (last_flag) counters[r * n_heads + h] = 0;
+      }
+      __syncthreads();
+      if (last_flag) {
+        __threadfence();
+        merge_partials<T, HD>(scratch + ((int64_t)r * n_heads + h) * n_splits * (HD + 2),
+                              out + (int64_t)r * ld_out + (int64_t)h * HD, n_splits, tid, TMA_THREADS);
+      }
+    }
+  }
+}
+
 template <typename T, int HD>
 int launch(const void* q, int64_t ld_q, void* out, int64_t ld_out, const int* row_seq, const int* row_pos,
            const int* page_table, int table_width, const void* k_pages, const void* v_pages, const void* k_new,
            const void* v_new, int64_t ld_new, float* scratch, int* counters, int n_rows, int n_heads, int n_kv_heads,
            int page_size, int n_splits, float scale, int window, cudaStream_t stream) {
   dim3 grid(n_splits, n_heads, n_rows);
-  kvad_launch(attention_decode_kernel<T, HD>, grid, dim3(DEC_THREADS), 0, stream,
-      (const T*)q, ld_q, (T*)out, ld_out, row_seq, row_pos, page_table, table_width, (T*)const_cast<void*>(k_pages),
-      (T*)const_cast<void*>(v_pages), (const T*)k_new, (const T*)v_new, ld_new, scratch, counters, n_heads, n_kv_heads,
-      page_size, n_splits, scale, window);
+  constexpr bool tma_form = (HD == 16 || HD == 32 || HD == 64 || HD == 128 || HD == 256) &&
+                            DecTile<T, HD>::SMEM <= 200 * 1024;      // two stages of 256-wide 32-bit rows do not fit
+  if (tma_form && page_size == TILE_KEYS && !g_force_plain) {
+    using D = DecTile<T, HD>;
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)D::SMEM);
+      if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "attention_decode: cannot reserve %zu bytes of shared memory: %s", D::SMEM, cudaGetErrorString(e));
+      configured = true;
+    }
+    kvad_launch(attention_decode_tma_kernel<T, HD>, grid, dim3(TMA_THREADS), D::SMEM, stream,
+        (const T*)q, ld_q, (T*)out, ld_out, row_seq, row_pos, page_table, table_width, (T*)const_cast<void*>(k_pages),
+        (T*)const_cast<void*>(v_pages), (const T*)k_new, (const T*)v_new, ld_new, scratch, counters, n_heads, n_kv_heads,
+        n_splits, scale, window);
+  } else {
+    kvad_launch(attention_decode_kernel<T, HD>, grid, dim3(DEC_THREADS), 0, stream,
+        (const T*)q, ld_q, (T*)out, ld_out, row_seq, row_pos, page_table, table_width, (T*)const_cast<void*>(k_pages),
+        (T*)const_cast<void*>(v_pages), (const T*)k_new, (const T*)v_new, ld_new, scratch, counters, n_heads, n_kv_heads,
+        page_size, n_splits, scale, window);
+  }
   KVAD_CHECK_LAUNCH("attention_decode");
   if (n_splits > 1 && counters == nullptr) {
     kvad_launch(attention_decode_merge_kernel<T, HD>, dim3(n_rows, n_heads), dim3(HD < 64 ? 32 : 64), 0, stream, (const float*)scratch, (T*)out, ld_out, n_heads, n_splits);
@@ -279,6 +558,18 @@ int launch(const void* q, int64_t ld_q, void* out, int64_t ld_out, const int* ro
 }
 
 }  // namespace
+
+// Tests: 1 keeps every head size on the kernel that loads through registers; 0 lets the head sizes
+// 16, 32, 64, 128 and 256 take the TMA-fed kernel.
+KVAD_EXPORT void kvad_attention_decode_force_plain(int on) { g_force_plain = on != 0; }
+
+// How many bounded waits of the TMA-fed kernel have run out (0 in a healthy run).  Synchronises the device.
+KVAD_EXPORT int kvad_attention_decode_status() {
+  int n = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&n, g_decode_timeouts, sizeof(int));
+  if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "attention_decode_status: %s", cudaGetErrorString(e));
+  return n;
+}
 
 // How many floats of scratch a call needs (0 with one split).
 KVAD_EXPORT int64_t kvad_attention_decode_scratch(int n_rows, int n_heads, int head_dim, int n_splits) {

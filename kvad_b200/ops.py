@@ -370,6 +370,25 @@ class Ops:
                              _ptr(uniform), _ptr(out), _stream()), h)
 
 
+def decode_force_plain(on: bool) -> None:
+    """Tests: keep the decode attention of every head size on the kernel that loads through registers."""
+    h = lib("attention_decode")
+    h.kvad_attention_decode_force_plain.argtypes = [c_int]
+    h.kvad_attention_decode_force_plain.restype = None
+    h.kvad_attention_decode_force_plain(int(bool(on)))
+
+
+def decode_wait_timeouts() -> int:
+    """How many bounded waits of the TMA-fed decode attention have run out (0 in a healthy run)."""
+    h = lib("attention_decode")
+    h.kvad_attention_decode_status.argtypes = []
+    h.kvad_attention_decode_status.restype = c_int
+    n = h.kvad_attention_decode_status()
+    if n < 0:
+        raise KernelError(h.kvad_last_error().decode("utf-8", "replace"))
+    return n
+
+
 def tcgen05_wait_timeouts() -> int:
     """How many bounded waits of the tensor-core linear kernel have run out (0 in a healthy run)."""
     h = lib("linear_tcgen05")

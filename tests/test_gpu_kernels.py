@@ -347,11 +347,22 @@ def test_argmax_first_of_equals_and_nan():
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("hd,n_heads,n_kv,window", [(16, 4, 4, 0), (48, 6, 2, 0), (64, 12, 12, 0), (80, 3, 1, 0),
                                                     (128, 2, 2, 50), (256, 2, 1, 0), (32, 5, 5, 64), (112, 2, 2, 0)])
-def test_attention_decode_split_keys(dtype, hd, n_heads, n_kv, window):
-    """The decode kernel at every split count gives what the plain reference gives; sequences of very unequal
-    length share a launch (an empty split, a single key, a page boundary)."""
+@pytest.mark.parametrize("form", ["tma", "registers"])
+def test_attention_decode_split_keys(dtype, hd, n_heads, n_kv, window, form):
+    """The decode kernel (both of its forms) at every split count gives what the plain reference gives; sequences
+    of very unequal length share a launch (an empty split, a single key, a page boundary)."""
+    from kvad_b200.ops import decode_force_plain, decode_wait_timeouts
     g = torch.Generator().manual_seed(7 * hd + n_heads)
     ops = Ops(DT[dtype])
+    decode_force_plain(form == "registers")
+    try:
+        _decode_split_case(ops, g, dtype, hd, n_heads, n_kv, window)
+    finally:
+        decode_force_plain(False)
+    assert decode_wait_timeouts() == 0
+
+
+def _decode_split_case(ops, g, dtype, hd, n_heads, n_kv, window):
     lens = [700, 1, 64, 65, 130]
     table, kp, vp, ks, vs = make_cache(g, dtype, len(lens), lens, n_kv, hd)
     row_seq = torch.arange(len(lens), dtype=torch.int32)

@@ -91,12 +91,87 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
   }
 }
 
+// The same for few, narrow rows (decoding): one warp per row, the row in registers (NI chunks of 8 per
+// lane, so widths up to NI * 256), sums met by shuffles only.  Gain and bias are parameters, not the
+// previous kernel's work: they are fetched before the dependent-launch wait.
+template <typename T, int NI>
+__global__ void __launch_bounds__(128)
+layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
+                      const void* __restrict__ gain, const void* __restrict__ bias, int params_f32,
+                      T* __restrict__ out, int n_rows, int width, float eps) {
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
+  float g[NI][8], b[NI][8];
+#pragma unroll
+  for (int i = 0; i < NI; ++i) {
+    const int k0 = (lane + 32 * i) * 8;
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      g[i][t] = k0 < width ? load_param(gain, k0 + t, params_f32) : 0.f;
+      b[i][t] = (k0 < width && bias) ? load_param(bias, k0 + t, params_f32) : 0.f;
+    }
+  }
+  pdl_wait();
+  if (r >= n_rows) return;
+  const float* xr = x + (int64_t)(row_index ? row_index[r] : r) * width;
+  float v[NI][8];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < NI; ++i) {
+    const int k0 = (lane + 32 * i) * 8;
+    if (k0 < width) {
+      const float4 a = *reinterpret_cast<const float4*>(xr + k0), c = *reinterpret_cast<const float4*>(xr + k0 + 4);
+      v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w; v[i][4] = c.x; v[i][5] = c.y; v[i][6] = c.z; v[i][7] = c.w;
+    } else {
+#pragma unroll
+      for (int t = 0; t < 8; ++t) v[i][t] = 0.f;
+    }
+#pragma unroll
+    for (int t = 0; t < 8; ++t) sum += v[i][t];
+  }
+  const float mean = warp_sum(sum) / (float)width;
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < NI; ++i) {
+    if ((lane + 32 * i) * 8 < width) {
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        const float d = v[i][t] - mean;
+        sq = fmaf(d, d, sq);
+      }
+    }
+  }
+  const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
+  T* o = out + (int64_t)r * width;
+#pragma unroll
+  for (int i = 0; i < NI; ++i) {
+    const int k0 = (lane + 32 * i) * 8;
+    if (k0 < width) {
+#pragma unroll
+      for (int t = 0; t < 8; ++t) o[k0 + t] = from_f32<T>((v[i][t] - mean) * inv * g[i][t] + b[i][t]);
+    }
+  }
+}
+
 KVAD_EXPORT int kvad_layernorm(int out_dtype, const float* x, const int* row_index, const void* gain,
                                const void* bias, int params_f32, void* out, int n_rows, int width,
                                float eps, cudaStream_t stream) {
   KVAD_REQUIRE(n_rows >= 0 && width > 0, "layernorm: bad sizes rows=%d width=%d", n_rows, width);
   KVAD_REQUIRE(gain != nullptr, "layernorm: no gain");
   if (n_rows == 0) return KVAD_OK;
+  if (n_rows <= 64 && width % 8 == 0 && width <= 1024 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    // few narrow rows: a warp per row
+    const dim3 grid((n_rows + 3) / 4), block(128);
+    if (out_dtype == KVAD_DTYPE_F32)
+      kvad_launch(layernorm_warp_kernel<float, 4>, grid, block, 0, stream, x, row_index, gain, bias, params_f32, (float*)out, n_rows, width, eps);
+    else if (out_dtype == KVAD_DTYPE_BF16)
+      kvad_launch(layernorm_warp_kernel<__nv_bfloat16, 4>, grid, block, 0, stream, x, row_index, gain, bias, params_f32, (__nv_bfloat16*)out, n_rows, width, eps);
+    else
+      KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "layernorm: unknown dtype %d", out_dtype);
+    KVAD_CHECK_LAUNCH("layernorm");
+    return KVAD_OK;
+  }
   const size_t smem = (size_t)width * sizeof(float);
   KVAD_REQUIRE(smem <= 200 * 1024, "layernorm: width %d does not fit shared memory (limit %d)", width, 200 * 1024 / 4);
   const int threads = width >= 1024 ? 256 : 128;

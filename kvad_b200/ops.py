@@ -53,6 +53,8 @@ _SIGNATURES = {
         "kvad_linear_tcgen05": [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int,
                                 c_int, c_int, c_void_p],
         "kvad_linear_tcgen05_status": [],
+        "kvad_linear_tcgen05_ln": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p,
+                                   c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p],
     },
     "attention_simt": {
         "kvad_attention_simt": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
@@ -155,6 +157,11 @@ class Ops:
         self.tensor_core_linear = dtype == torch.bfloat16 and "linear_tcgen05" in build.sources()
         self.tensor_core_prefill = dtype == torch.bfloat16 and "attention_prefill" in build.sources()
         self.fast_decode = dtype == torch.bfloat16 and "attention_decode" in build.sources()
+        # One kernel for `layernorm -> linear` (at most 16 rows).  Measured on a B200 it is SLOWER than the
+        # pair under dependent launch (GPT-2 small, batch 8: 0.55 ms a step against 0.50 ms): the separate
+        # norm already hides behind the product's weight fetch, while the fused kernel puts the norm on every
+        # CTA's critical path.  So it is off unless KVAD_FUSE_NORM=1 (or this flag) turns it on.
+        self.fuse_norm = os.environ.get("KVAD_FUSE_NORM", "0") == "1"
         self._counters = None       # zeroed ints the decode kernel counts finished splits in (left zeroed by it)
 
     # -- embedding -----------------------------------------------------------------
@@ -227,6 +234,41 @@ class Ops:
         h = lib("linear_simt")
         _check(h.kvad_linear_simt(self.code, _ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k,
                                   epi, _stream()), h)
+
+    def ln_linear_takes(self, n_rows: int, k: int, epilogue: str) -> bool:
+        """Whether `layernorm -> linear` of these sizes runs as one kernel (few rows, bfloat16 tensor-core path,
+        a storing epilogue, and the normalised rows fitting shared memory beside the weights)."""
+        return (self.fuse_norm and self.tensor_core_linear and 1 <= n_rows <= 16 and k % 8 == 0 and k <= 2048
+                and epilogue != "residual")
+
+    def layernorm_linear(self, x, rows, n_rows: int, gain, beta, eps: float, weight, bias, out, epilogue: str = "store") -> None:
+        """out = epilogue(layernorm(x[rows]) . weight^T + bias) in one kernel; x is the float32 residual stream."""
+        _need_cuda(x, rows, gain, beta, weight, bias, out)
+        epi = EPILOGUES[epilogue]
+        if epilogue == "residual" or not (1 <= n_rows <= 16):
+            raise KernelError("layernorm_linear: takes 1..16 rows and a storing epilogue")
+        n, k = weight.shape
+        ldo = _rows_view(out, "linear output")
+        if x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1 or x.shape[1] != k:
+            raise KernelError("layernorm_linear: input must be the float32 residual stream of the weight's width")
+        if weight.dtype != torch.bfloat16 or not weight.is_contiguous():
+            raise KernelError("layernorm_linear: weight must be contiguous bfloat16")
+        want_out = torch.float32 if epi == 4 else torch.bfloat16
+        if out.dtype != want_out or tuple(out.shape) != (n_rows, n):
+            raise KernelError(f"layernorm_linear: output must be {want_out} of shape [{n_rows}, {n}]")
+        if gain.numel() != k or (beta is not None and (beta.numel() != k or beta.dtype != gain.dtype)):
+            raise KernelError("layernorm_linear: gain and bias of the norm must have the row's width and one dtype")
+        if rows is not None and (rows.dtype != torch.int32 or rows.numel() < n_rows):
+            raise KernelError("layernorm_linear: row list must be int32, one per row")
+        if rows is None and x.shape[0] < n_rows:
+            raise KernelError("layernorm_linear: fewer input rows than asked for")
+        bias_f32 = 1 if (bias is not None and bias.dtype == torch.float32) else 0
+        if bias is not None and bias.numel() != n:
+            raise KernelError(f"layernorm_linear: bias has {bias.numel()} entries for {n} outputs")
+        h = lib("linear_tcgen05")
+        _check(h.kvad_linear_tcgen05_ln(_ptr(x), x.stride(0), _ptr(rows), _ptr(gain), _ptr(beta),
+                                        1 if gain.dtype == torch.float32 else 0, float(eps), _ptr(weight), _ptr(bias),
+                                        bias_f32, _ptr(out), ldo, int(n_rows), n, k, epi, _stream()), h)
 
     # -- cache writes and attention --------------------------------------------------
     def kv_store(self, k_src, v_src, row_seq, row_pos, page_table, k_pages, v_pages) -> None:

@@ -24,6 +24,8 @@ from .linear import Linear
 
 
 class CausalSelfAttention(Mixer):
+    accepts_deferred_norm = True       # `h` goes straight into the fused projection
+
     def __init__(self, prefix: str, width: int, n_heads: int, head_dim: int, score_scale: float,
                  n_kv_heads: Optional[int] = None, window: Optional[int] = None, bias: bool = True,
                  stored: str = "out_in", qkv_name: str = "qkv.", out_name: str = "out.",

@@ -238,3 +238,21 @@ def test_dependent_launch_changes_no_result(engines, plains):
     assert np.array_equal(outs[(True, "float32")], outs[(False, "float32")])
     ref = plains("A", "bfloat16").logits(t)
     assert rel_err(outs[(True, "bfloat16")], ref) < TOL["bfloat16"] and rel_err(outs[(False, "bfloat16")], ref) < TOL["bfloat16"]
+
+
+def test_norm_fused_into_the_product_changes_no_result(engines, plains):
+    """Decoding with `layernorm -> linear` as one kernel (an option, off by default) gives the same logits."""
+    e, plain = engines("B", "bfloat16"), plains("B", "bfloat16")
+    t = random_tokens(960, 40, 1000)
+    ref = plain.logits(t)
+    try:
+        for fused in (True, False):
+            e.ops.fuse_norm = fused
+            s = e.open()
+            e.step([StepEntry(s, t[:30], [])])
+            for j in range(30, 40):
+                got = e.step([StepEntry(s, [t[j]], [0])]).cpu().numpy()
+                assert rel_err(got[0], ref[j]) < TOL["bfloat16"], (fused, j)
+            e.close(s)
+    finally:
+        e.ops.fuse_norm = False

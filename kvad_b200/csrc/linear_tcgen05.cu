@@ -51,6 +51,8 @@ constexpr uint32_t WAIT_LIMIT = 1u << 24;
 constexpr int SMEM_BUDGET = 200 * 1024;
 
 __device__ int g_wait_timeouts = 0;
+bool g_no_3d = false;               // tests: keep the swapped form on one TMA load per K block
+bool g_force_3d = false;            // tests: take the grouped three-dimensional loads at every row count
 
 template <int BN> struct Tile {
   static constexpr uint32_t A_BYTES = BM * BK * 2;
@@ -92,6 +94,16 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
 
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -116,8 +128,8 @@ __device__ __forceinline__ uint64_t sw128_desc(uint32_t smem_addr) {
 }
 
 // bfloat16 x bfloat16 -> float32, both K-major, M = 128, N = BN.
-template <int BN> __device__ __forceinline__ constexpr uint32_t instr_desc() {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+template <int BN, int M_ROWS = BM> __device__ __forceinline__ constexpr uint32_t instr_desc() {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(M_ROWS >> 4) << 24);
 }
 
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
@@ -215,7 +227,12 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   uint64_t* tmem_full_bar = empty_bar + STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
 
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 32) {
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_w);
+  }
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
   const int kb_total = (K + BK - 1) / BK;
   const int kb_begin = blockIdx.z * kb_per_split;
@@ -237,7 +254,6 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  pdl_launch_dependents();
   if (warp == 0) {
     if (lane == 0) {
       // weights do not depend on the kernel before: their first stages are on the way before the wait
@@ -313,8 +329,8 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 // in the tensor-memory lanes and the activation rows in its columns, so a warp of the epilogue holds
 // 32 consecutive outputs of one activation row and writes them side by side.
 // ---------------------------------------------------------------------------------------------
-template <int MB> struct SkinnyTile {
-  static constexpr uint32_t W_BYTES = BM * BK * 2;
+template <int MB, int TM> struct SkinnyTile {
+  static constexpr uint32_t W_BYTES = TM * BK * 2;
   static constexpr uint32_t A_BYTES = MB * BK * 2;
   static constexpr int STAGES_RAW = SMEM_BUDGET / (W_BYTES + A_BYTES);
   static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
@@ -322,12 +338,14 @@ template <int MB> struct SkinnyTile {
   static constexpr size_t SMEM = (size_t)STAGES * (W_BYTES + A_BYTES) + (2 * STAGES + 1) * 8 + 16 + 1024;
 };
 
-template <int MB, int EPI>
+// TM = 128 or 64 weight rows per CTA.  With 64 the accumulator sits in tensor-memory lanes
+// (row % 16) + 32 * (row / 16): the first 16 lanes of each of the four warps' quarters.
+template <int MB, int EPI, int TM>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 linear_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                              const void* __restrict__ bias, int bias_f32, void* __restrict__ out, int64_t ldo,
                              int M, int N, int K, int kb_per_split) {
-  using T = SkinnyTile<MB>;
+  using T = SkinnyTile<MB, TM>;
   constexpr int STAGES = T::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -338,8 +356,13 @@ linear_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __
   uint64_t* tmem_full_bar = empty_bar + STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
 
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BM;
+  if (threadIdx.x == 32) {
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_w);
+  }
+  const int n0 = blockIdx.x * TM;
   const int kb_total = (K + BK - 1) / BK;
   const int kb_begin = blockIdx.y * kb_per_split;
   const int kb_end = kb_begin + kb_per_split < kb_total ? kb_begin + kb_per_split : kb_total;
@@ -360,7 +383,6 @@ linear_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  pdl_launch_dependents();
   if (warp == 0) {
     if (lane == 0) {
       // this CTA's weights (often all of them) are requested before the kernel before has finished
@@ -383,7 +405,7 @@ linear_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc<MB>();
+      constexpr uint32_t idesc = instr_desc<MB, TM>();
       for (int i = 0; i < num_kb; ++i) {
         const int s = i % STAGES;
         const uint32_t phase = (i / STAGES) & 1;
@@ -400,7 +422,8 @@ linear_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __
     }
   } else {
     const int quarter = warp & 3;
-    const int n = n0 + quarter * 32 + lane;
+    const bool has_row = TM == 128 || lane < 16;
+    const int n = has_row ? n0 + (TM == 128 ? quarter * 32 + lane : quarter * 16 + lane) : N;
     float b = 0.f;                                   // a parameter: fetched while the product is still running
     if (blockIdx.y == 0 && bias != nullptr && n < N) b = load_param(bias, n, bias_f32);
     pdl_wait();
@@ -442,6 +465,151 @@ linear_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __
   if (warp == 1) {
     __syncwarp();
     tmem_dealloc(tmem_base, T::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The swapped form with few, large TMA loads (K a multiple of 64).  Timing the form above showed its
+// cost to grow with the NUMBER of 64-wide K blocks a CTA walks (about 0.3 us each), not with their
+// bytes or their MMAs: every block costs two TMA instructions and a barrier round trip.  Here the
+// matrices are described to TMA as three-dimensional, [K/64][rows][64], so that ONE instruction
+// brings the CTA's whole share of the activations (all its K blocks) and one brings a group of G
+// K blocks of 128 weight rows (64 KB for G = 4); a CTA of the qkv product issues 4 loads instead of 24.
+// ---------------------------------------------------------------------------------------------
+constexpr int W_GROUP = 4;          // K blocks of weights per TMA instruction and pipeline stage
+
+template <int MB, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+linear_tcgen05_skinny3d_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                               const void* __restrict__ bias, int bias_f32, void* __restrict__ out, int64_t ldo,
+                               int M, int N, int K, int kb_per_split, int stages) {
+  constexpr uint32_t W_BYTES = BM * BK * 2;            // one K block of 128 weight rows
+  constexpr uint32_t A_BYTES = MB * BK * 2;            // one K block of the activation rows
+  constexpr int TMEM_COLS = MB < 32 ? 32 : MB;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* a_all = smem;                                               // kb_per_split blocks
+  uint8_t* w_ring = smem + (size_t)kb_per_split * A_BYTES;             // stages x W_GROUP blocks
+  uint64_t* w_full = reinterpret_cast<uint64_t*>(w_ring + (size_t)stages * W_GROUP * W_BYTES);
+  uint64_t* w_empty = w_full + stages;
+  uint64_t* a_full = w_empty + stages;
+  uint64_t* tmem_full_bar = a_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 32) {
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_w);
+  }
+  const int n0 = blockIdx.x * BM;
+  const int kb_total = K / BK;
+  const int kb_begin = blockIdx.y * kb_per_split;
+  const int kb_end = kb_begin + kb_per_split < kb_total ? kb_begin + kb_per_split : kb_total;
+  const int num_kb = kb_end - kb_begin;
+  const int n_groups = (num_kb + W_GROUP - 1) / W_GROUP;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&w_full[s], 1);
+      mbar_init(&w_empty[s], 1);
+    }
+    mbar_init(a_full, 1);
+    mbar_init(tmem_full_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const int pre = n_groups < stages ? n_groups : stages;
+      for (int g = 0; g < pre; ++g) {                      // weights: before the dependent-launch wait
+        mbar_expect_tx(&w_full[g], W_GROUP * W_BYTES);
+        tma_load_3d(w_ring + (size_t)g * W_GROUP * W_BYTES, &map_w, &w_full[g], 0, n0, kb_begin + g * W_GROUP);
+      }
+      pdl_wait();
+      mbar_expect_tx(a_full, (uint32_t)kb_per_split * A_BYTES);
+      tma_load_3d(a_all, &map_a, a_full, 0, 0, kb_begin);
+      for (int g = pre; g < n_groups; ++g) {
+        const int s = g % stages;
+        if (!mbar_wait(&w_empty[s], ((g / stages) & 1) ^ 1)) break;
+        mbar_expect_tx(&w_full[s], W_GROUP * W_BYTES);
+        tma_load_3d(w_ring + (size_t)s * W_GROUP * W_BYTES, &map_w, &w_full[s], 0, n0, kb_begin + g * W_GROUP);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc<MB>();
+      bool ok = mbar_wait(a_full, 0);
+      for (int g = 0; g < n_groups && ok; ++g) {
+        const int s = g % stages;
+        ok = mbar_wait(&w_full[s], (g / stages) & 1);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int j = 0; j < W_GROUP; ++j) {
+          const int kb = g * W_GROUP + j;
+          if (kb < num_kb) {
+            const uint64_t w_desc = sw128_desc(smem_u32(w_ring + ((size_t)s * W_GROUP + j) * W_BYTES));
+            const uint64_t a_desc = sw128_desc(smem_u32(a_all + (size_t)kb * A_BYTES));
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              umma(tmem_base, w_desc + (uint64_t)(k * 2), a_desc + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(&w_empty[s]);
+      }
+      umma_commit(tmem_full_bar);
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int n = n0 + quarter * 32 + lane;
+    float b = 0.f;
+    if (blockIdx.y == 0 && bias != nullptr && n < N) b = load_param(bias, n, bias_f32);
+    pdl_wait();
+    const bool ok = mbar_wait(tmem_full_bar, 0);
+    tc_fence_after();
+    if (ok) {
+      const bool atomic = gridDim.y > 1;
+#pragma unroll 1
+      for (int c = 0; c < MB; c += 16) {
+        float v[16];
+        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, v);
+        if (n < N && c < M) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = c + j;
+            if (m < M) {
+              float t = v[j] + b;
+              if (EPI == EPI_GELU_TANH) t = gelu_tanh(t);
+              if (EPI == EPI_GELU_ERF) t = gelu_erf(t);
+              const int64_t o = (int64_t)m * ldo + n;
+              if (EPI == EPI_STORE || EPI == EPI_GELU_TANH || EPI == EPI_GELU_ERF) {
+                reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(t);
+              } else if (EPI == EPI_RESIDUAL) {
+                if (atomic) atomicAdd(reinterpret_cast<float*>(out) + o, t);
+                else reinterpret_cast<float*>(out)[o] += t;
+              } else {
+                reinterpret_cast<float*>(out)[o] = t;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -726,6 +894,33 @@ int tensor_map(const void* ptr, int64_t ld, int rows, int cols, int box_rows, CU
   return KVAD_OK;
 }
 
+// The same matrix seen as [cols / 64][rows][64], loaded in boxes of depth x box_rows x 64 (cols a multiple of 64).
+int tensor_map_3d(const void* ptr, int64_t ld, int rows, int cols, int box_rows, int depth, CUtensorMap* out) {
+  MapKey key{ptr, ld, rows, cols, box_rows + (depth << 16) + (1 << 30)};
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) {
+    *out = it->second;
+    return KVAD_OK;
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) KVAD_FAIL(KVAD_ERR_CUDA, "linear_tcgen05: the driver does not offer cuTensorMapEncodeTiled");
+  cuuint64_t dims[3] = {(cuuint64_t)BK, (cuuint64_t)rows, (cuuint64_t)(cols / BK)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)BK * 2};
+  cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, (cuuint32_t)depth};
+  cuuint32_t elem[3] = {1, 1, 1};
+  CUtensorMap m;
+  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    KVAD_FAIL(KVAD_ERR_CUDA, "linear_tcgen05: cuTensorMapEncodeTiled (3-D) failed (%d) for a [%d, %d] matrix with row stride %lld", (int)r, rows, cols, (long long)ld);
+  if (g_maps.size() > 8192) g_maps.clear();
+  g_maps.emplace(key, m);
+  *out = m;
+  return KVAD_OK;
+}
+
 template <int BN, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, const void* bias, int bias_f32, void* out, int64_t ldo,
            int M, int N, int K, int splits, cudaStream_t stream) {
@@ -758,34 +953,62 @@ int launch_epi(int epilogue, const CUtensorMap& ma, const CUtensorMap& mw, const
   KVAD_FAIL(KVAD_ERR_ARGUMENT, "linear_tcgen05: unknown epilogue %d", epilogue);
 }
 
-template <int MB, int EPI>
+template <int MB, int EPI, int TM>
 int launch_skinny(const CUtensorMap& ma, const CUtensorMap& mw, const void* bias, int bias_f32, void* out, int64_t ldo,
                   int M, int N, int K, int splits, cudaStream_t stream) {
-  using T = SkinnyTile<MB>;
+  using T = SkinnyTile<MB, TM>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(linear_tcgen05_skinny_kernel<MB, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::SMEM);
+    cudaError_t e = cudaFuncSetAttribute(linear_tcgen05_skinny_kernel<MB, EPI, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::SMEM);
     if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "linear_tcgen05: cannot reserve %zu bytes of shared memory: %s", T::SMEM, cudaGetErrorString(e));
     configured = true;
   }
   const int kb_total = (K + BK - 1) / BK;
   const int kb_per_split = (kb_total + splits - 1) / splits;
   const int z = (kb_total + kb_per_split - 1) / kb_per_split;
-  dim3 grid((N + BM - 1) / BM, z);
-  kvad_launch(linear_tcgen05_skinny_kernel<MB, EPI>, grid, dim3(NUM_THREADS), T::SMEM, stream, ma, mw, bias, bias_f32, out, ldo, M, N, K, kb_per_split);
+  dim3 grid((N + TM - 1) / TM, z);
+  kvad_launch(linear_tcgen05_skinny_kernel<MB, EPI, TM>, grid, dim3(NUM_THREADS), T::SMEM, stream, ma, mw, bias, bias_f32, out, ldo, M, N, K, kb_per_split);
   KVAD_CHECK_LAUNCH("linear_tcgen05_skinny");
   return KVAD_OK;
 }
 
-template <int MB>
+template <int MB, int TM>
 int launch_skinny_epi(int epilogue, const CUtensorMap& ma, const CUtensorMap& mw, const void* bias, int bias_f32,
                       void* out, int64_t ldo, int M, int N, int K, int splits, cudaStream_t stream) {
   switch (epilogue) {
-    case EPI_STORE: return launch_skinny<MB, EPI_STORE>(ma, mw, bias, bias_f32, out, ldo, M, N, K, 1, stream);
-    case EPI_GELU_TANH: return launch_skinny<MB, EPI_GELU_TANH>(ma, mw, bias, bias_f32, out, ldo, M, N, K, 1, stream);
-    case EPI_GELU_ERF: return launch_skinny<MB, EPI_GELU_ERF>(ma, mw, bias, bias_f32, out, ldo, M, N, K, 1, stream);
-    case EPI_RESIDUAL: return launch_skinny<MB, EPI_RESIDUAL>(ma, mw, bias, bias_f32, out, ldo, M, N, K, splits, stream);
-    case EPI_STORE_F32: return launch_skinny<MB, EPI_STORE_F32>(ma, mw, bias, bias_f32, out, ldo, M, N, K, 1, stream);
+    case EPI_STORE: return launch_skinny<MB, EPI_STORE, TM>(ma, mw, bias, bias_f32, out, ldo, M, N, K, 1, stream);
+    case EPI_GELU_TANH: return launch_skinny<MB, EPI_GELU_TANH, TM>(ma, mw, bias, bias_f32, out, ldo, M, N, K, 1, stream);
+    case EPI_GELU_ERF: return launch_skinny<MB, EPI_GELU_ERF, TM>(ma, mw, bias, bias_f32, out, ldo, M, N, K, 1, stream);
+    case EPI_RESIDUAL: return launch_skinny<MB, EPI_RESIDUAL, TM>(ma, mw, bias, bias_f32, out, ldo, M, N, K, splits, stream);
+    case EPI_STORE_F32: return launch_skinny<MB, EPI_STORE_F32, TM>(ma, mw, bias, bias_f32, out, ldo, M, N, K, 1, stream);
+  }
+  KVAD_FAIL(KVAD_ERR_ARGUMENT, "linear_tcgen05: unknown epilogue %d", epilogue);
+}
+
+template <int MB, int EPI>
+int launch_skinny3d(const CUtensorMap& ma, const CUtensorMap& mw, const void* bias, int bias_f32, void* out, int64_t ldo,
+                    int M, int N, int K, int kb_per_split, int z, int stages, size_t smem, cudaStream_t stream) {
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(linear_tcgen05_skinny3d_kernel<MB, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "linear_tcgen05: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = smem;
+  }
+  kvad_launch(linear_tcgen05_skinny3d_kernel<MB, EPI>, dim3((N + BM - 1) / BM, z), dim3(NUM_THREADS), smem, stream, ma, mw,
+              bias, bias_f32, out, ldo, M, N, K, kb_per_split, stages);
+  KVAD_CHECK_LAUNCH("linear_tcgen05_skinny3d");
+  return KVAD_OK;
+}
+
+template <int MB>
+int launch_skinny3d_epi(int epilogue, const CUtensorMap& ma, const CUtensorMap& mw, const void* bias, int bias_f32, void* out,
+                        int64_t ldo, int M, int N, int K, int kb_per_split, int z, int stages, size_t smem, cudaStream_t stream) {
+  switch (epilogue) {
+    case EPI_STORE: return launch_skinny3d<MB, EPI_STORE>(ma, mw, bias, bias_f32, out, ldo, M, N, K, kb_per_split, z, stages, smem, stream);
+    case EPI_GELU_TANH: return launch_skinny3d<MB, EPI_GELU_TANH>(ma, mw, bias, bias_f32, out, ldo, M, N, K, kb_per_split, z, stages, smem, stream);
+    case EPI_GELU_ERF: return launch_skinny3d<MB, EPI_GELU_ERF>(ma, mw, bias, bias_f32, out, ldo, M, N, K, kb_per_split, z, stages, smem, stream);
+    case EPI_RESIDUAL: return launch_skinny3d<MB, EPI_RESIDUAL>(ma, mw, bias, bias_f32, out, ldo, M, N, K, kb_per_split, z, stages, smem, stream);
+    case EPI_STORE_F32: return launch_skinny3d<MB, EPI_STORE_F32>(ma, mw, bias, bias_f32, out, ldo, M, N, K, kb_per_split, z, stages, smem, stream);
   }
   KVAD_FAIL(KVAD_ERR_ARGUMENT, "linear_tcgen05: unknown epilogue %d", epilogue);
 }
@@ -858,7 +1081,8 @@ KVAD_EXPORT int kvad_linear_tcgen05_ln(const float* x, int64_t ldx, const int* r
 
 // `force` fixes what the kernel otherwise chooses (tests): bits 0-15 the tile width of the wide
 // form (16, 32, 64, 128 or 256); bits 16-23 how many CTAs share K (residual epilogue only);
-// bits 24-25 the form: 1 wide (activation rows on the M side), 2 swapped (at most 64 rows).
+// bits 24-25 the form: 1 wide (activation rows on the M side), 2 swapped (at most 64 rows; the
+// tile width then means weight rows per CTA, 64 or 128).
 KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, const void* bias, int bias_f32,
                                     void* out, int64_t ldo, int M, int N, int K, int epilogue, int force,
                                     cudaStream_t stream) {
@@ -874,10 +1098,12 @@ KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, c
   const int force_bn = force & 0xffff, force_splits = (force >> 16) & 0xff, force_path = (force >> 24) & 3;
   KVAD_REQUIRE(force_path != 2 || M <= 64, "linear_tcgen05: the swapped form takes at most 64 rows, not %d", M);
   if ((M <= 64 && force_path != 1 && force_bn == 0) || force_path == 2) {
-    // few rows: weights on the M side of the MMA
+    // few rows: weights on the M side of the MMA, 64 rows a CTA unless that makes more CTAs than SMs
     const int mb = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     const int kb_all = (K + BK - 1) / BK;
-    const int tiles = (N + BM - 1) / BM;
+    int tm = ((N + BM - 1) / BM < 74) ? 64 : 128;
+    if (force_bn == 64 || force_bn == 128) tm = force_bn;
+    const int tiles = (N + tm - 1) / tm;
     int sp = 1;
     if (epilogue == EPI_RESIDUAL) {
       sp = force_splits > 0 ? force_splits : (148 + tiles - 1) / tiles;
@@ -885,16 +1111,59 @@ KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, c
       if (sp > kb_all) sp = kb_all;
       if (sp < 1) sp = 1;
     }
+    if (K % BK == 0 && force_bn == 0 && !g_no_3d && (mb == 16 || g_force_3d)) {
+      // (with more activation rows their resident copy leaves room for one stage of weights only,
+      // and the form above, which pipelines block by block, is the faster one: measured at 64 rows)
+      // K in whole blocks of 64: few, large, three-dimensional TMA loads
+      const int tiles128 = (N + BM - 1) / BM;
+      int sp3 = 1;
+      if (epilogue == EPI_RESIDUAL) {
+        sp3 = force_splits > 0 ? force_splits : (148 + tiles128 - 1) / tiles128;
+        if (sp3 > 16) sp3 = 16;
+        if (sp3 > kb_all) sp3 = kb_all;
+        if (sp3 < 1) sp3 = 1;
+      }
+      const int kb_per_split = (kb_all + sp3 - 1) / sp3;
+      const int z = (kb_all + kb_per_split - 1) / kb_per_split;
+      const size_t a_bytes = (size_t)kb_per_split * mb * BK * 2;
+      const size_t stage_bytes = (size_t)W_GROUP * BM * BK * 2;
+      const int groups = (kb_per_split + W_GROUP - 1) / W_GROUP;
+      if (a_bytes + stage_bytes + 2048 <= (size_t)SMEM_BUDGET && kb_per_split <= 256) {
+        int stages3 = (int)(((size_t)SMEM_BUDGET - a_bytes - 2048) / stage_bytes);
+        if (stages3 > groups) stages3 = groups;
+        if (stages3 > 3) stages3 = 3;
+        const size_t smem3 = a_bytes + (size_t)stages3 * stage_bytes + (2 * stages3 + 2) * 8 + 16 + 1024;
+        CUtensorMap ma3, mw3;
+        int rc3 = tensor_map_3d(A, lda, M, K, mb, kb_per_split, &ma3);
+        if (rc3 != KVAD_OK) return rc3;
+        rc3 = tensor_map_3d(W, K, N, K, BM, W_GROUP, &mw3);
+        if (rc3 != KVAD_OK) return rc3;
+        switch (mb) {
+          case 16: return launch_skinny3d_epi<16>(epilogue, ma3, mw3, bias, bias_f32, out, ldo, M, N, K, kb_per_split, z, stages3, smem3, stream);
+          case 32: return launch_skinny3d_epi<32>(epilogue, ma3, mw3, bias, bias_f32, out, ldo, M, N, K, kb_per_split, z, stages3, smem3, stream);
+          default: return launch_skinny3d_epi<64>(epilogue, ma3, mw3, bias, bias_f32, out, ldo, M, N, K, kb_per_split, z, stages3, smem3, stream);
+        }
+      }
+    }
     CUtensorMap ma, mw;
     int rc = tensor_map(A, lda, M, K, mb, &ma);
     if (rc != KVAD_OK) return rc;
-    rc = tensor_map(W, K, N, K, BM, &mw);
+    rc = tensor_map(W, K, N, K, tm, &mw);
     if (rc != KVAD_OK) return rc;
-    switch (mb) {
-      case 16: return launch_skinny_epi<16>(epilogue, ma, mw, bias, bias_f32, out, ldo, M, N, K, sp, stream);
-      case 32: return launch_skinny_epi<32>(epilogue, ma, mw, bias, bias_f32, out, ldo, M, N, K, sp, stream);
-      default: return launch_skinny_epi<64>(epilogue, ma, mw, bias, bias_f32, out, ldo, M, N, K, sp, stream);
+#define KVAD_SKINNY(MBV, TMV) return launch_skinny_epi<MBV, TMV>(epilogue, ma, mw, bias, bias_f32, out, ldo, M, N, K, sp, stream)
+    if (tm == 64) {
+      switch (mb) {
+        case 16: KVAD_SKINNY(16, 64);
+        case 32: KVAD_SKINNY(32, 64);
+        default: KVAD_SKINNY(64, 64);
+      }
     }
+    switch (mb) {
+      case 16: KVAD_SKINNY(16, 128);
+      case 32: KVAD_SKINNY(32, 128);
+      default: KVAD_SKINNY(64, 128);
+    }
+#undef KVAD_SKINNY
   }
   const int m_tiles = (M + BM - 1) / BM;
   int bn = force_bn;
@@ -938,6 +1207,10 @@ KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, c
     default: return launch_epi<256>(epilogue, ma, mw, bias, bias_f32, out, ldo, M, N, K, splits, stream);
   }
 }
+
+// Tests: 1 keeps the swapped form on two-dimensional loads (one per K block) for every K; 2 takes the
+// grouped three-dimensional loads whenever K allows; 0 is the kernel's own choice (them, up to 16 rows).
+KVAD_EXPORT void kvad_linear_tcgen05_no_3d(int on) { g_no_3d = on == 1; g_force_3d = on == 2; }
 
 // How many bounded waits have run out since the library was loaded (0 in a healthy run).
 // Synchronises the device.

@@ -431,6 +431,15 @@ def decode_wait_timeouts() -> int:
     return n
 
 
+def tcgen05_load_form(mode: int) -> None:
+    """Tests: 0 lets the swapped linear kernel choose between one TMA load per K block and grouped
+    three-dimensional loads; 1 forces the former, 2 the latter (where K is a multiple of 64)."""
+    h = lib("linear_tcgen05")
+    h.kvad_linear_tcgen05_no_3d.argtypes = [c_int]
+    h.kvad_linear_tcgen05_no_3d.restype = None
+    h.kvad_linear_tcgen05_no_3d(int(mode))
+
+
 def tcgen05_wait_timeouts() -> int:
     """How many bounded waits of the tensor-core linear kernel have run out (0 in a healthy run)."""
     h = lib("linear_tcgen05")

@@ -171,11 +171,18 @@ def test_linear_tensor_cores_swapped_form(m):
     ops = Ops(torch.bfloat16)
     if not ops.tensor_core_linear:
         pytest.skip("tensor-core linear kernel not built")
-    from kvad_b200.ops import tcgen05_wait_timeouts
+    from kvad_b200.ops import tcgen05_load_form, tcgen05_wait_timeouts
     g = torch.Generator().manual_seed(70 + m)
     for n, k in [(768, 768), (1000, 96), (50, 320), (2304, 64), (777, 3072), (50257, 768)]:
         for epi in ("store", "gelu_tanh", "gelu_erf", "residual", "store_f32"):
-            assert linear_case(ops, "bfloat16", m, n, k, epi, g, form="swapped") < KTOL["bfloat16"], (m, n, k, epi)
+            try:
+                for mode in (0, 1, 2):        # the kernel's choice; one load per K block; grouped 3-D loads
+                    tcgen05_load_form(mode)
+                    assert linear_case(ops, "bfloat16", m, n, k, epi, g, form="swapped") < KTOL["bfloat16"], (m, n, k, epi, mode)
+            finally:
+                tcgen05_load_form(0)
+            for tile in (64, 128):          # weight rows per CTA
+                assert linear_case(ops, "bfloat16", m, n, k, epi, g, form="swapped", tile=tile) < KTOL["bfloat16"], (m, n, k, epi, tile)
         for splits in (1, 2, 5, 16):
             assert linear_case(ops, "bfloat16", m, n, k, "residual", g, form="swapped", splits=splits) < KTOL["bfloat16"]
     assert linear_case(ops, "bfloat16", m, 333, 128, "store", g, bias=False, strided=True, form="swapped") < KTOL["bfloat16"]

@@ -191,6 +191,7 @@ def main():
     ap.add_argument("--layers", type=int, default=GPT2_SMALL["n_layer"], help="fewer layers than GPT-2 small has (named in config)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profiling)")
+    ap.add_argument("--phase", default="all", choices=["all", "prefill"], help="`prefill`: only the 2 x 1024-token prefill (profiling)")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64, prefill and e2e (quick runs)")
     args = ap.parse_args()
 
@@ -221,6 +222,13 @@ def main():
     engine.use_graphs = not args.no_graphs
     print(f"[bench] {engine.describe()}", file=sys.stderr)
 
+    if args.phase == "prefill":
+        t_ms = prefill_point(engine, 2, 1024, iters=3, warmup=3, seed=3)
+        fl = prefill_flops(cfg, args.layers, 2, 1024, 2)
+        print(json.dumps({"phase": "prefill", "tokens": 2048, "ms": round(t_ms, 4), "tokens_per_s": round(2048 / (t_ms * 1e-3), 1),
+                          "tflops": round(fl / (t_ms * 1e-3) / 1e12, 2), "frac": round(fl / (t_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                          "of": pk_src}))
+        return 0
     main_pt = decode_point(engine, args.batch, args.prompt_len, args.steps, warmup, seed=1, clock=True)
     bytes_step = decode_bytes(engine, args.batch, main_pt["mean_ctx"])
     achieved = bytes_step / (main_pt["ms_per_step"] * 1e-3) / 1e9

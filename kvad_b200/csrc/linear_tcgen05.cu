@@ -47,20 +47,26 @@ constexpr int BM = 128;
 constexpr int BK = 64;              // 64 bfloat16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;    // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
+constexpr int NUM_THREADS_WIDE = 320;   // the wide form has eight epilogue warps: two per quarter of the tensor-memory lanes
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 constexpr int SMEM_BUDGET = 200 * 1024;
+constexpr int SMEM_BUDGET_WIDE = 192 * 1024;     // the wide form keeps 33 KB for its output slabs
 
 __device__ int g_wait_timeouts = 0;
 bool g_no_3d = false;               // tests: keep the swapped form on one TMA load per K block
+bool g_no_tma_out = false;          // tests: the wide form writes its output with plain stores
 bool g_force_3d = false;            // tests: take the grouped three-dimensional loads at every row count
 
 template <int BN> struct Tile {
   static constexpr uint32_t A_BYTES = BM * BK * 2;
   static constexpr uint32_t B_BYTES = BN * BK * 2;
-  static constexpr int STAGES_RAW = SMEM_BUDGET / (A_BYTES + B_BYTES);
+  static constexpr int STAGES_RAW = SMEM_BUDGET_WIDE / (A_BYTES + B_BYTES);
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
-  static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + (2 * STAGES + 1) * 8 + 16 + 1024;
+  // after the stages: the barriers, the bias of this tile as floats, and one 4 KB slab per epilogue warp
+  // from which TMA stores (or reduce-adds) 32 rows x 128 bytes of output at a time
+  static constexpr size_t SLAB_OFFSET = (((size_t)STAGES * (A_BYTES + B_BYTES) + (2 * STAGES + 1) * 8 + 16 + BN * 4) + 1023) / 1024 * 1024;
+  static constexpr size_t SMEM = SLAB_OFFSET + 8 * 4096 + 1024;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -99,6 +105,20 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, u
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
 }
+
+// 32 rows x 128 bytes from a swizzled slab in shared memory to the output tensor, clipped at its edges.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
+}
+// The same, added to what the tensor holds (float32): the residual sum without a read in the kernel.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
@@ -156,6 +176,16 @@ __device__ __forceinline__ void tmem_ld16(uint32_t addr, float* v) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// tanh-form GELU with the hardware tanh (tanh.approx.f32, relative error about 2^-11): the result is
+// rounded to bfloat16 (8 bits of mantissa) right after, and the exact tanhf costs the epilogue of the
+// up-projection several times what its whole product costs.
+__device__ __forceinline__ float gelu_tanh_fast(float t) {
+  const float c = 0.79788456f;
+  float th;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(c * (t + 0.044715f * t * t * t)));
+  return 0.5f * t * (1.0f + th);
+}
+
 // One chunk of CH consecutive columns of one output row.
 template <int EPI, int CH>
 __device__ __forceinline__ void store_chunk(const float* v, void* out, int64_t ldo, int row, int col0, int N,
@@ -165,7 +195,7 @@ __device__ __forceinline__ void store_chunk(const float* v, void* out, int64_t l
   for (int j = 0; j < CH; ++j) {
     float t = v[j];
     if (add_bias && bias != nullptr && col0 + j < N) t += load_param(bias, col0 + j, bias_f32);
-    if (EPI == EPI_GELU_TANH) t = gelu_tanh(t);
+    if (EPI == EPI_GELU_TANH) t = gelu_tanh_fast(t);
     if (EPI == EPI_GELU_ERF) t = gelu_erf(t);
     x[j] = t;
   }
@@ -212,8 +242,9 @@ __device__ __forceinline__ void store_chunk(const float* v, void* out, int64_t l
 }
 
 template <int BN, int EPI>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS_WIDE, 1)
 linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                      const __grid_constant__ CUtensorMap map_out, int tma_out,
                       const void* __restrict__ bias, int bias_f32, void* __restrict__ out, int64_t ldo,
                       int M, int N, int K, int kb_per_split) {
   using T = Tile<BN>;
@@ -232,6 +263,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   if (threadIdx.x == 32) {
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_w);
+    if (tma_out) prefetch_tensormap(&map_out);
   }
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
   const int kb_total = (K + BK - 1) / BK;
@@ -298,18 +330,83 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   } else {
     const int quarter = warp & 3;       // the 32 tensor-memory lanes this warp may read
     const int row = m0 + quarter * 32 + lane;
+    if (tma_out) {                        // this tile's bias, as floats, while the product runs
+      float* bias_st = reinterpret_cast<float*>(tmem_slot + 4);
+      for (int j = threadIdx.x - 64; j < BN; j += NUM_THREADS_WIDE - 64)
+        bias_st[j] = (bias != nullptr && n0 + j < N) ? load_param(bias, n0 + j, bias_f32) : 0.f;
+      asm volatile("bar.sync 1, 256;" ::: "memory");     // the eight epilogue warps
+    }
     pdl_wait();
     const bool ok = mbar_wait(tmem_full_bar, 0);
     tc_fence_after();
     if (ok) {
       const bool add_bias = blockIdx.z == 0;
       const bool atomic = gridDim.z > 1;
+      // two warps share a quarter of the lanes: the first takes the left half of the columns, the second the right
+      constexpr int HALF = BN >= 32 ? BN / 2 : BN;
+      const int c_begin = (BN >= 32 && warp >= 6) ? HALF : 0;
+      const int c_end = (BN >= 32) ? c_begin + HALF : (warp >= 6 ? 0 : BN);
+      if (tma_out) {
+        // ---- through a slab in shared memory, out by TMA: whole 128-byte rows, no read-modify-write here
+        constexpr bool F32_OUT = (EPI == EPI_RESIDUAL || EPI == EPI_STORE_F32);
+        constexpr int SLAB_COLS = F32_OUT ? 32 : 64;              // 128 bytes of output per row
+        uint8_t* slab = smem + T::SLAB_OFFSET + (size_t)(warp - 2) * 4096;
+        const float* bias_sh = reinterpret_cast<const float*>(tmem_slot + 4);
+        // the two warps of a quarter take alternate slabs
+        const int first = (warp >= 6 ? 1 : 0) * SLAB_COLS;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
-        float v[16];
-        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, v);   // all lanes take part
-        if (row < M && n0 + c < N)
-          store_chunk<EPI, 16>(v, out, ldo, row, n0 + c, N, bias, bias_f32, add_bias, atomic);
+        for (int c0 = first; c0 < BN; c0 += 2 * SLAB_COLS) {
+          if (c0 > first) {                                         // the slab's last journey has been read
+            if (lane == 0) bulk_wait_read();
+            __syncwarp();
+          }
+#pragma unroll
+          for (int cc = 0; cc < SLAB_COLS; cc += 16) {
+            float v[16];
+            tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c0 + cc), v);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float t = v[j] + (add_bias ? bias_sh[c0 + cc + j] : 0.f);
+              if (EPI == EPI_GELU_TANH) t = gelu_tanh_fast(t);
+              if (EPI == EPI_GELU_ERF) t = gelu_erf(t);
+              v[j] = t;
+            }
+            if (F32_OUT) {
+#pragma unroll
+              for (int j = 0; j < 16; j += 4) {
+                const int chunk = (cc + j) >> 2;                   // 16-byte piece of the 128-byte row
+                *reinterpret_cast<float4*>(slab + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; j += 8) {
+                const int chunk = (cc + j) >> 3;
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]), p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                uint4 q;
+                q.x = *reinterpret_cast<uint32_t*>(&p0); q.y = *reinterpret_cast<uint32_t*>(&p1);
+                q.z = *reinterpret_cast<uint32_t*>(&p2); q.w = *reinterpret_cast<uint32_t*>(&p3);
+                *reinterpret_cast<uint4*>(slab + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = q;
+              }
+            }
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0 && n0 + c0 < N && m0 + quarter * 32 < M) {
+            if (EPI == EPI_RESIDUAL) tma_reduce_add_2d(&map_out, slab, n0 + c0, m0 + quarter * 32);
+            else tma_store_2d(&map_out, slab, n0 + c0, m0 + quarter * 32);
+            bulk_commit();
+          }
+        }
+        if (lane == 0) bulk_wait_all();
+      } else {
+#pragma unroll 1
+        for (int c = c_begin; c < c_end; c += 16) {
+          float v[16];
+          tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, v);   // all lanes take part
+          if (row < M && n0 + c < N)
+            store_chunk<EPI, 16>(v, out, ldo, row, n0 + c, N, bias, bias_f32, add_bias, atomic);
+        }
       }
     }
   }
@@ -441,7 +538,7 @@ linear_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __
             const int m = c + j;
             if (m < M) {
               float t = v[j] + b;
-              if (EPI == EPI_GELU_TANH) t = gelu_tanh(t);
+              if (EPI == EPI_GELU_TANH) t = gelu_tanh_fast(t);
               if (EPI == EPI_GELU_ERF) t = gelu_erf(t);
               const int64_t o = (int64_t)m * ldo + n;
               if (EPI == EPI_STORE || EPI == EPI_GELU_TANH || EPI == EPI_GELU_ERF) {
@@ -586,7 +683,7 @@ linear_tcgen05_skinny3d_kernel(const __grid_constant__ CUtensorMap map_a, const 
             const int m = c + j;
             if (m < M) {
               float t = v[j] + b;
-              if (EPI == EPI_GELU_TANH) t = gelu_tanh(t);
+              if (EPI == EPI_GELU_TANH) t = gelu_tanh_fast(t);
               if (EPI == EPI_GELU_ERF) t = gelu_erf(t);
               const int64_t o = (int64_t)m * ldo + n;
               if (EPI == EPI_STORE || EPI == EPI_GELU_TANH || EPI == EPI_GELU_ERF) {
@@ -806,7 +903,7 @@ linear_tcgen05_ln_kernel(const __grid_constant__ CUtensorMap map_w, const float*
             const int m = c + j;
             if (m < M) {
               float t = v[j] + b;
-              if (EPI == EPI_GELU_TANH) t = gelu_tanh(t);
+              if (EPI == EPI_GELU_TANH) t = gelu_tanh_fast(t);
               if (EPI == EPI_GELU_ERF) t = gelu_erf(t);
               const int64_t o = (int64_t)m * ldo + n;
               if (EPI == EPI_STORE_F32) reinterpret_cast<float*>(out)[o] = t;
@@ -894,6 +991,34 @@ int tensor_map(const void* ptr, int64_t ld, int rows, int cols, int box_rows, CU
   return KVAD_OK;
 }
 
+// An output matrix [rows, cols] with row stride ld, written in boxes of 32 rows x 128 bytes.
+int tensor_map_out(const void* ptr, int64_t ld, int rows, int cols, bool f32, CUtensorMap* out) {
+  MapKey key{ptr, ld, rows, cols, f32 ? -32 : -64};
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) {
+    *out = it->second;
+    return KVAD_OK;
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) KVAD_FAIL(KVAD_ERR_CUDA, "linear_tcgen05: the driver does not offer cuTensorMapEncodeTiled");
+  const int elem_bytes = f32 ? 4 : 2;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * elem_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), 32};
+  cuuint32_t elem[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = fn(&m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr),
+                  dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    KVAD_FAIL(KVAD_ERR_CUDA, "linear_tcgen05: cuTensorMapEncodeTiled failed (%d) for an output of [%d, %d] with row stride %lld", (int)r, rows, cols, (long long)ld);
+  if (g_maps.size() > 8192) g_maps.clear();
+  g_maps.emplace(key, m);
+  *out = m;
+  return KVAD_OK;
+}
+
 // The same matrix seen as [cols / 64][rows][64], loaded in boxes of depth x box_rows x 64 (cols a multiple of 64).
 int tensor_map_3d(const void* ptr, int64_t ld, int rows, int cols, int box_rows, int depth, CUtensorMap* out) {
   MapKey key{ptr, ld, rows, cols, box_rows + (depth << 16) + (1 << 30)};
@@ -925,6 +1050,16 @@ template <int BN, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, const void* bias, int bias_f32, void* out, int64_t ldo,
            int M, int N, int K, int splits, cudaStream_t stream) {
   using T = Tile<BN>;
+  // out by TMA where its rules hold: a 16-byte aligned base and row stride (not the 50257-wide logits)
+  constexpr bool f32_out = (EPI == EPI_RESIDUAL || EPI == EPI_STORE_F32);
+  const int elem_bytes = f32_out ? 4 : 2;
+  CUtensorMap mo = ma;
+  int tma_out = 0;
+  if (BN >= 64 && !g_no_tma_out && (ldo * elem_bytes) % 16 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    int rc = tensor_map_out(out, ldo, M, N, f32_out, &mo);
+    if (rc != KVAD_OK) return rc;
+    tma_out = 1;
+  }
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(linear_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::SMEM);
@@ -935,7 +1070,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, const void* bias, int b
   const int kb_per_split = (kb_total + splits - 1) / splits;
   const int z = (kb_total + kb_per_split - 1) / kb_per_split;
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, z);
-  kvad_launch(linear_tcgen05_kernel<BN, EPI>, grid, dim3(NUM_THREADS), T::SMEM, stream, ma, mw, bias, bias_f32, out, ldo, M, N, K, kb_per_split);
+  kvad_launch(linear_tcgen05_kernel<BN, EPI>, grid, dim3(NUM_THREADS_WIDE), T::SMEM, stream, ma, mw, mo, tma_out, bias, bias_f32, out, ldo, M, N, K, kb_per_split);
   KVAD_CHECK_LAUNCH("linear_tcgen05");
   return KVAD_OK;
 }
@@ -1211,6 +1346,9 @@ KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, c
 // Tests: 1 keeps the swapped form on two-dimensional loads (one per K block) for every K; 2 takes the
 // grouped three-dimensional loads whenever K allows; 0 is the kernel's own choice (them, up to 16 rows).
 KVAD_EXPORT void kvad_linear_tcgen05_no_3d(int on) { g_no_3d = on == 1; g_force_3d = on == 2; }
+
+// Tests: 1 makes the wide form write its output with plain stores instead of TMA stores / reduce-adds.
+KVAD_EXPORT void kvad_linear_tcgen05_no_tma_out(int on) { g_no_tma_out = on != 0; }
 
 // How many bounded waits have run out since the library was loaded (0 in a healthy run).
 // Synchronises the device.

@@ -91,7 +91,7 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
   }
 }
 
-// The same for few, narrow rows (decoding): one warp per row, the row in registers (NI chunks of 8 per
+// The same for narrow rows: one warp per row, the row in registers (NI chunks of 8 per
 // lane, so widths up to NI * 256), sums met by shuffles only.  Gain and bias are parameters, not the
 // previous kernel's work: they are fetched before the dependent-launch wait.
 template <typename T, int NI>
@@ -160,8 +160,8 @@ KVAD_EXPORT int kvad_layernorm(int out_dtype, const float* x, const int* row_ind
   KVAD_REQUIRE(n_rows >= 0 && width > 0, "layernorm: bad sizes rows=%d width=%d", n_rows, width);
   KVAD_REQUIRE(gain != nullptr, "layernorm: no gain");
   if (n_rows == 0) return KVAD_OK;
-  if (n_rows <= 64 && width % 8 == 0 && width <= 1024 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
-    // few narrow rows: a warp per row
+  if (width % 8 == 0 && width <= 1024 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    // narrow rows: a warp per row
     const dim3 grid((n_rows + 3) / 4), block(128);
     if (out_dtype == KVAD_DTYPE_F32)
       kvad_launch(layernorm_warp_kernel<float, 4>, grid, block, 0, stream, x, row_index, gain, bias, params_f32, (float*)out, n_rows, width, eps);
@@ -217,6 +217,31 @@ __global__ void kv_store_kernel(const T* __restrict__ k_src, const T* __restrict
   }
 }
 
+// The same in 16-byte pieces (head sizes are multiples of 8 elements of 2 bytes, or 4 of 4 bytes).
+template <typename T>
+__global__ void kv_store_vec_kernel(const T* __restrict__ k_src, const T* __restrict__ v_src, int64_t ld_src,
+                                    const int* __restrict__ row_seq, const int* __restrict__ row_pos,
+                                    const int* __restrict__ page_table, int table_width,
+                                    T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                    int n_rows, int n_kv_heads, int head_dim, int page_size) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int E = 16 / (int)sizeof(T);                 // elements per piece
+  const int pieces_per_head = head_dim / E, pieces_per_row = n_kv_heads * pieces_per_head;
+  const int64_t total = (int64_t)n_rows * pieces_per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / pieces_per_row), p = (int)(i % pieces_per_row);
+    const int h = p / pieces_per_head, d = (p % pieces_per_head) * E;
+    const int pos = row_pos[r];
+    const int page = page_table[(int64_t)row_seq[r] * table_width + pos / page_size];
+    const int64_t dst = (((int64_t)page * n_kv_heads + h) * page_size + pos % page_size) * head_dim + d;
+    const int64_t src = (int64_t)r * ld_src + (int64_t)h * head_dim + d;
+    *reinterpret_cast<uint4*>(k_pages + dst) = *reinterpret_cast<const uint4*>(k_src + src);
+    *reinterpret_cast<uint4*>(v_pages + dst) = *reinterpret_cast<const uint4*>(v_src + src);
+  }
+}
+
 KVAD_EXPORT int kvad_kv_store(int dtype, const void* k_src, const void* v_src, int64_t ld_src,
                               const int* row_seq, const int* row_pos, const int* page_table,
                               int table_width, void* k_pages, void* v_pages, int n_rows,
@@ -224,15 +249,25 @@ KVAD_EXPORT int kvad_kv_store(int dtype, const void* k_src, const void* v_src, i
   KVAD_REQUIRE(n_rows >= 0 && n_kv_heads > 0 && head_dim > 0 && page_size > 0 && table_width > 0,
                "kv_store: bad sizes rows=%d kv_heads=%d head_dim=%d page=%d table=%d", n_rows, n_kv_heads, head_dim, page_size, table_width);
   if (n_rows == 0) return KVAD_OK;
-  const int64_t total = (int64_t)n_rows * n_kv_heads * head_dim;
+  const int elem = dtype == KVAD_DTYPE_F32 ? 4 : 2;
+  const int per = 16 / elem;
+  const bool vec = head_dim % per == 0 && ld_src % per == 0 &&
+                   ((reinterpret_cast<uintptr_t>(k_src) | reinterpret_cast<uintptr_t>(v_src) |
+                     reinterpret_cast<uintptr_t>(k_pages) | reinterpret_cast<uintptr_t>(v_pages)) & 15) == 0;
+  const int64_t total = (int64_t)n_rows * n_kv_heads * head_dim / (vec ? per : 1);
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
-  if (dtype == KVAD_DTYPE_F32)
-    kvad_launch(kv_store_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)k_src, (const float*)v_src, ld_src, row_seq, row_pos, page_table, table_width, (float*)k_pages, (float*)v_pages, n_rows, n_kv_heads, head_dim, page_size);
-  else if (dtype == KVAD_DTYPE_BF16)
-    kvad_launch(kv_store_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)k_src, (const __nv_bfloat16*)v_src, ld_src, row_seq, row_pos, page_table, table_width, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, n_rows, n_kv_heads, head_dim, page_size);
-  else
+#define KVAD_KV(KERNEL, T)                                                                                            \
+  kvad_launch(KERNEL<T>, dim3(blocks), dim3(threads), 0, stream, (const T*)k_src, (const T*)v_src, ld_src, row_seq,   \
+              row_pos, page_table, table_width, (T*)k_pages, (T*)v_pages, n_rows, n_kv_heads, head_dim, page_size)
+  if (dtype == KVAD_DTYPE_F32) {
+    if (vec) KVAD_KV(kv_store_vec_kernel, float); else KVAD_KV(kv_store_kernel, float);
+  } else if (dtype == KVAD_DTYPE_BF16) {
+    if (vec) KVAD_KV(kv_store_vec_kernel, __nv_bfloat16); else KVAD_KV(kv_store_kernel, __nv_bfloat16);
+  } else {
     KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "kv_store: unknown dtype %d", dtype);
+  }
+#undef KVAD_KV
   KVAD_CHECK_LAUNCH("kv_store");
   return KVAD_OK;
 }

@@ -13,6 +13,7 @@ counterpart there and follows the names of `Llm` (crates/llm/src/runtime.rs).
 """
 from __future__ import annotations
 
+import collections
 import os
 import sys
 import tempfile
@@ -82,9 +83,6 @@ class _SampleBuffers:
 class _DecodePlan:
     def __init__(self, meta: DeviceMeta, bufs: _SampleBuffers):
         self.meta, self.bufs = meta, bufs
-        self.graphs: dict = {}
-        self.warmed: dict = {}
-        self.launches: dict = {}
 
 
 class Engine:
@@ -109,7 +107,9 @@ class Engine:
         self._sample_bufs = None
         self.eos_token_ids = tuple(model.plan.eos_token_ids)
         self.verbose = verbose
-        self.use_graphs = True
+        self.use_graphs = model.graph_safe     # a part that reads host-side step data keeps the model on plain launches
+        self.max_graphs = 48            # captured step shapes kept (least recently used go first)
+        self._graphs: "collections.OrderedDict" = collections.OrderedDict()
         self._decode_plans: dict = {}
         self.h2d_bytes = 0          # bytes copied host -> device by steps and sampling (for measurement)
         self.d2h_bytes = 0
@@ -222,11 +222,52 @@ class Engine:
         Returns float32 logits `[wanted rows, vocab]` in the order of the entries
         and of their `want` lists.  The tensor is scratch: it is valid until the
         next step.  A step that is refused (unknown slot, token outside the
-        vocabulary, full context, full cache) changes nothing."""
+        vocabulary, full context, full cache) changes nothing.
+
+        A step's kernels depend only on its shape (rows, sequences, the longest
+        run of new rows, wanted rows), never on positions or lengths, which live
+        in device memory.  So the second time a shape is seen its launch sequence
+        is captured as a CUDA graph and later steps of that shape replay it: one
+        upload and one launch instead of a launch per kernel from the host."""
         ctx = self.begin_step(entries)
-        logits = self.model.forward(ctx)
+        b = ctx.batch
+        key = ("step", b.n_rows, b.n_seqs, b.max_new, ctx.n_want, id(ctx.meta), self.arena.generation)
+        logits = self._replay_or_run(key, lambda: self.model.forward(ctx))
         self.end_step(ctx)
         return logits
+
+    def _replay_or_run(self, key, body):
+        """Runs `body` (a sequence of kernel launches on fixed addresses) kernel by kernel the first
+        time `key` is seen, captures it the second time, replays it from then on.  Returns what
+        `body` returned when it was captured (tensors at fixed addresses)."""
+        from .. import ops as ops_mod
+        if not self.use_graphs:
+            return body()
+        hit = self._graphs.get(key)
+        if hit is not None and hit != "seen":
+            graph, result, n_kernels = hit
+            self._graphs.move_to_end(key)
+            graph.replay()
+            self.graph_kernels += n_kernels
+            return result
+        if hit is None:
+            self._graphs[key] = "seen"
+            while len(self._graphs) > self.max_graphs:
+                self._graphs.popitem(last=False)
+            before = ops_mod.launch_count()
+            result = body()
+            self.graph_kernels += ops_mod.launch_count() - before
+            return result
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = ops_mod.launch_count()
+        with torch.cuda.graph(graph):
+            result = body()
+        n_kernels = ops_mod.launch_count() - before
+        self._graphs[key] = (graph, result, n_kernels)
+        graph.replay()
+        self.graph_kernels += n_kernels
+        return result
 
     # -- sampling on the device ----------------------------------------------------------
     def _sampling_buffers(self, n: int):
@@ -257,7 +298,7 @@ class Engine:
 
     def step_and_sample(self, entries, samplers) -> list[int]:
         """The generation loop's backend call: last-row logits of each entry, then a token each."""
-        if self.use_graphs and all(len(toks) == 1 for _, toks in entries):
+        if all(len(toks) == 1 for _, toks in entries):
             plan = self._decode(entries, samplers)
             return plan.bufs.read(len(entries), self)
         logits = self.step([StepEntry(slot, toks, (len(toks) - 1,)) for slot, toks in entries])
@@ -267,9 +308,7 @@ class Engine:
     def _decode(self, entries, samplers, *, device_fed: bool = False) -> "_DecodePlan":
         """One token per sequence, then a token chosen for each; leaves the chosen tokens on the device
         (in `plan.bufs.out`, and in the token section of the plan's metadata, ready to be the next
-        step's input).  The first step of a batch size runs kernel by kernel; the second captures a
-        CUDA graph; later ones replay it: one upload and one launch per step."""
-        from .. import ops as ops_mod
+        step's input).  Captured and replayed like any other step shape: one upload and one launch."""
         n = len(entries)
         plan = self._decode_plans.get(n)
         if plan is None:
@@ -280,24 +319,8 @@ class Engine:
         ctx = self.begin_step([StepEntry(slot, toks, (0,)) for slot, toks in entries], meta=plan.meta,
                               keep_tokens=device_fed)
         greedy = plan.bufs.load(samplers, self)
-        key = (greedy, self.arena.generation)
-        graph = plan.graphs.get(key)
-        if graph is None and plan.warmed.get(key) and self.use_graphs:
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            before = ops_mod.launch_count()
-            with torch.cuda.graph(graph):
-                self._decode_body(ctx, plan, greedy)
-            plan.launches[key] = ops_mod.launch_count() - before
-            plan.graphs[key] = graph
-        if graph is not None:
-            graph.replay()
-            self.graph_kernels += plan.launches[key]
-        else:
-            before = ops_mod.launch_count()
-            self._decode_body(ctx, plan, greedy)
-            self.graph_kernels += ops_mod.launch_count() - before
-            plan.warmed[key] = True
+        key = ("decode", n, greedy, id(plan.meta), self.arena.generation)
+        self._replay_or_run(key, lambda: self._decode_body(ctx, plan, greedy))
         self.end_step(ctx)
         return plan
 

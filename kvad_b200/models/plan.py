@@ -82,6 +82,11 @@ class Model:
     def max_positions(self) -> Optional[int]:
         return self.embedding.max_positions
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether every part's launches depend on a step's shape only (see `Part.graph_safe`)."""
+        return all(p.all_graph_safe() for p in self.parts())
+
     # -- weights -------------------------------------------------------------------
     def parts(self):
         return [self.embedding, *self.blocks, self.head]

@@ -440,6 +440,14 @@ def tcgen05_load_form(mode: int) -> None:
     h.kvad_linear_tcgen05_no_3d(int(mode))
 
 
+def tcgen05_plain_stores(on: bool) -> None:
+    """Tests: the wide linear kernel writes its output with plain stores instead of TMA stores / reduce-adds."""
+    h = lib("linear_tcgen05")
+    h.kvad_linear_tcgen05_no_tma_out.argtypes = [c_int]
+    h.kvad_linear_tcgen05_no_tma_out.restype = None
+    h.kvad_linear_tcgen05_no_tma_out(int(bool(on)))
+
+
 def tcgen05_wait_timeouts() -> int:
     """How many bounded waits of the tensor-core linear kernel have run out (0 in a healthy run)."""
     h = lib("linear_tcgen05")

@@ -24,6 +24,8 @@ from .linear import Linear
 
 
 class CausalSelfAttention(Mixer):
+    graph_safe = True
+
     accepts_deferred_norm = True       # `h` goes straight into the fused projection
 
     def __init__(self, prefix: str, width: int, n_heads: int, head_dim: int, score_scale: float,

@@ -82,8 +82,17 @@ Fetch = Callable[..., torch.Tensor]   # fetch(name, transpose=False, keep_f32=Fa
 class Part:
     """Base of all parts: tensor requests, loading, accounting."""
 
+    #: True if what the part launches for a step depends only on the step's SHAPE (rows, sequences,
+    #: longest run of new rows, wanted rows) and on device memory - never on host-side values such as
+    #: positions, lengths or slot ids.  Steps of a model whose parts all say so are captured as CUDA
+    #: graphs and replayed.  A part that loops over host data leaves this False and runs kernel by kernel.
+    graph_safe = False
+
     def __init__(self, prefix: str = ""):
         self.prefix = prefix
+
+    def all_graph_safe(self) -> bool:
+        return bool(self.graph_safe) and all(c.all_graph_safe() for c in self.children())
 
     def children(self) -> list["Part"]:
         return []

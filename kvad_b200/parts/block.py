@@ -8,6 +8,8 @@ from .base import Block, PartSpec, build_part, register_part
 
 
 class PreNormBlock(Block):
+    graph_safe = True
+
     def __init__(self, prefix: str, norm1: PartSpec, mixer: PartSpec, norm2: PartSpec, feed_forward: PartSpec,
                  norm1_name: str = "norm1.", mixer_name: str = "mixer.", norm2_name: str = "norm2.",
                  feed_forward_name: str = "ff."):

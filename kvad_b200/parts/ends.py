@@ -20,6 +20,8 @@ from .linear import Linear
 
 
 class TokenEmbedding(Part):
+    graph_safe = True
+
     def __init__(self, prefix: str, vocab_size: int, width: int, name: str = "wte.weight",
                  position: Optional[PartSpec] = None):
         super().__init__(prefix)
@@ -51,6 +53,8 @@ class TokenEmbedding(Part):
 
 
 class LMHead(Part):
+    graph_safe = True
+
     def __init__(self, prefix: str, vocab_size: int, width: int, norm: PartSpec, tied: bool,
                  norm_name: str = "ln_f.", name: str = "lm_head.", bias: bool = False,
                  embedding: Optional[TokenEmbedding] = None):

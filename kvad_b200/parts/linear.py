@@ -17,6 +17,8 @@ from .base import DeferredNorm, Part
 
 
 class Linear(Part):
+    graph_safe = True
+
     def __init__(self, prefix: str, in_features: int, out_features: int, *, bias: bool = True,
                  stored: str = "out_in", shared_weight: Optional[torch.Tensor] = None,
                  bias_optional: bool = False, has_weight: bool = True):

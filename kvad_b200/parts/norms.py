@@ -10,6 +10,8 @@ from .base import Norm, register_part
 
 
 class LayerNorm(Norm):
+    graph_safe = True
+
     def __init__(self, prefix: str, width: int, eps: float, bias: bool = True):
         super().__init__(prefix)
         self.width, self.eps, self.has_bias = int(width), float(eps), bias

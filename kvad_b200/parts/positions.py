@@ -13,6 +13,8 @@ from .base import PositionEncoding, register_part
 
 
 class LearnedAbsolute(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, prefix: str, n_positions: int, width: int, name: str = "wpe.weight"):
         super().__init__(prefix)
         self.max_positions, self.width, self.name = int(n_positions), int(width), name
@@ -32,6 +34,8 @@ class LearnedAbsolute(PositionEncoding):
 
 
 class NoPositions(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, prefix: str = ""):
         super().__init__(prefix)
 

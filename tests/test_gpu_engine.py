@@ -256,3 +256,23 @@ def test_norm_fused_into_the_product_changes_no_result(engines, plains):
             e.close(s)
     finally:
         e.ops.fuse_norm = False
+
+
+def test_repeated_step_shapes_replay_a_graph_with_the_same_result(engines, plains):
+    """The second prompt step of a shape is captured, the third replays: all three give the oracle's logits,
+    although positions, lengths and pages differ between them."""
+    e, plain = engines("B", "bfloat16"), plains("B", "bfloat16")
+    assert e.use_graphs
+    before = len([v for v in e._graphs.values() if v != "seen"])
+    for rep in range(4):
+        a, b = random_tokens(970 + rep, 50, 1000), random_tokens(980 + rep, 21, 1000)
+        sa, sb = e.open(), e.open()
+        pre = 7 * rep                                  # the same shape of step at other positions
+        if pre:
+            e.step([StepEntry(sa, a[:pre], []), StepEntry(sb, b[:1], [])])
+        got = e.step([StepEntry(sa, a[pre:pre + 20], [19]), StepEntry(sb, b[1 if pre else 0:][:20], [0, 19])]).cpu().numpy()
+        off = 1 if pre else 0
+        ref = np.stack([plain.logits(a[:pre + 20])[pre + 19], plain.logits(b[:off + 20])[off], plain.logits(b[:off + 20])[off + 19]])
+        assert rel_err(got, ref) < TOL["bfloat16"], rep
+        e.close(sa), e.close(sb)
+    assert len([v for v in e._graphs.values() if v != "seen"]) > before

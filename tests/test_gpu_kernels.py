@@ -150,18 +150,29 @@ def test_linear_tensor_cores_shapes(m):
     assert tcgen05_wait_timeouts() == 0
 
 
+@pytest.mark.parametrize("stores", ["tma", "plain"])
 @pytest.mark.parametrize("tile", [16, 32, 64, 128, 256])
-def test_linear_tensor_cores_every_tile_and_split(tile):
+def test_linear_tensor_cores_every_tile_and_split(tile, stores):
+    """Every tile width of the wide form, every split of K, output by TMA store / reduce-add and by plain stores."""
     ops = Ops(torch.bfloat16)
     if not ops.tensor_core_linear:
         pytest.skip("tensor-core linear kernel not built")
+    from kvad_b200.ops import tcgen05_plain_stores
+    tcgen05_plain_stores(stores == "plain")
+    try:
+        _every_tile_and_split(ops, tile)
+    finally:
+        tcgen05_plain_stores(False)
+
+
+def _every_tile_and_split(ops, tile):
     from kvad_b200.ops import tcgen05_wait_timeouts
     g = torch.Generator().manual_seed(50 + tile)
-    for m, n, k in [(5, 1000, 96), (200, 515, 832), (130, 257, 3072)]:
-        for epi in ("store", "gelu_tanh", "residual", "store_f32"):
-            assert linear_case(ops, "bfloat16", m, n, k, epi, g, tile=tile) < KTOL["bfloat16"], (m, n, k, epi)
+    for m, n, k in [(5, 1000, 96), (200, 515, 832), (130, 257, 3072), (300, 768, 128), (129, 1024, 64)]:
+        for epi in ("store", "gelu_tanh", "gelu_erf", "residual", "store_f32"):
+            assert linear_case(ops, "bfloat16", m, n, k, epi, g, tile=tile, form="wide") < KTOL["bfloat16"], (m, n, k, epi)
         for splits in (1, 2, 3, 7):
-            assert linear_case(ops, "bfloat16", m, n, k, "residual", g, tile=tile, splits=splits) < KTOL["bfloat16"], (m, n, k, splits)
+            assert linear_case(ops, "bfloat16", m, n, k, "residual", g, tile=tile, splits=splits, form="wide") < KTOL["bfloat16"], (m, n, k, splits)
     assert tcgen05_wait_timeouts() == 0
 
 

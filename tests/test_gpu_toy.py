@@ -130,6 +130,7 @@ def toy_dir(tmp_path):
 def test_toy_mixer_with_state_is_registered_built_and_stepped(toy_dir):
     d, tensors = toy_dir
     e = Engine.from_pretrained(d, "float32", max_tokens=1024)
+    assert not e.use_graphs         # the toy mixer walks host-side step data, so its model is never captured as a graph
     layout = e.model.cache_layout
     assert len(layout.groups) == 2 and len(layout.state_groups) == 1 and len(layout.kv_groups) == 1
     assert [g.entries for g in layout.groups] == [(0, 2), (1,)]           # the two toy layers share a group of their own

@@ -1300,33 +1300,33 @@ KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, c
     }
 #undef KVAD_SKINNY
   }
+  // Tile width and K split by a small cost model fitted to measurements on a B200: a CTA pays a fixed
+  // cost (set-up, filling the pipeline, the epilogue: larger for wider tiles) plus about 0.27 us per
+  // 64-wide block of K whatever the tile's width (the ring of stages is bound by the latency of its
+  // round trip, so a wide tile gets its extra work for free), and the grid runs in waves of 148 CTAs.
   const int m_tiles = (M + BM - 1) / BM;
-  int bn = force_bn;
-  if (bn == 0) {
-    bn = 16;
-    const int candidates[5] = {256, 128, 64, 32, 16};
+  const int kb_total = (K + BK - 1) / BK;
+  int bn = force_bn, splits = 1;
+  {
+    const int widths[5] = {256, 128, 64, 32, 16};
+    const float fixed_us[5] = {7.0f, 4.0f, 3.0f, 2.6f, 2.5f};
+    float best = 1e30f;
     for (int i = 0; i < 5; ++i) {
-      const int c = candidates[i];
-      if ((int64_t)m_tiles * ((N + c - 1) / c) >= 132) { bn = c; break; }
+      if (force_bn != 0 && widths[i] != force_bn) continue;
+      const int64_t tiles = (int64_t)m_tiles * ((N + widths[i] - 1) / widths[i]);
+      for (int sp = 1; sp <= 8; sp *= 2) {
+        if (sp > 1 && (epilogue != EPI_RESIDUAL || kb_total / sp < 2)) break;
+        if (force_splits > 0 && sp != 1) break;
+        const int64_t waves = (tiles * sp + 147) / 148;
+        const float t = (float)waves * ((float)((kb_total + sp - 1) / sp) * 0.27f + fixed_us[i]);
+        if (t < best) { best = t; bn = widths[i]; splits = sp; }
+      }
     }
   }
   KVAD_REQUIRE(bn == 16 || bn == 32 || bn == 64 || bn == 128 || bn == 256, "linear_tcgen05: tile width %d is not one of 16, 32, 64, 128, 256", bn);
-  const int kb_total = (K + BK - 1) / BK;
-  int splits = 1;
-  if (epilogue == EPI_RESIDUAL) {
-    if (force_splits > 0) {
-      splits = force_splits;
-    } else {
-      const int64_t tiles = (int64_t)m_tiles * ((N + bn - 1) / bn);
-      if (tiles < 100 && kb_total >= 4) {
-        splits = (int)((148 + tiles - 1) / tiles);
-        if (splits > kb_total / 2) splits = kb_total / 2;
-        if (splits > 16) splits = 16;
-      }
-    }
-    if (splits > kb_total) splits = kb_total;
-    if (splits < 1) splits = 1;
-  }
+  if (epilogue == EPI_RESIDUAL && force_splits > 0) splits = force_splits;
+  if (splits > kb_total) splits = kb_total;
+  if (splits < 1) splits = 1;
 
   CUtensorMap ma, mw;
   int rc = tensor_map(A, lda, M, K, BM, &ma);

@@ -91,6 +91,40 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
   }
 }
 
+__device__ __forceinline__ void store8(float* o, const float* y) {
+  *reinterpret_cast<float4*>(o) = make_float4(y[0], y[1], y[2], y[3]);
+  *reinterpret_cast<float4*>(o + 4) = make_float4(y[4], y[5], y[6], y[7]);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* o, const float* y) {
+  __nv_bfloat162 p0 = __floats2bfloat162_rn(y[0], y[1]), p1 = __floats2bfloat162_rn(y[2], y[3]);
+  __nv_bfloat162 p2 = __floats2bfloat162_rn(y[4], y[5]), p3 = __floats2bfloat162_rn(y[6], y[7]);
+  uint4 q;
+  q.x = *reinterpret_cast<uint32_t*>(&p0); q.y = *reinterpret_cast<uint32_t*>(&p1);
+  q.z = *reinterpret_cast<uint32_t*>(&p2); q.w = *reinterpret_cast<uint32_t*>(&p3);
+  *reinterpret_cast<uint4*>(o) = q;
+}
+
+// Eight consecutive parameters (32-bit or bfloat16) in one or two 16-byte loads; zeros if `take` is false.
+__device__ __forceinline__ void load_params8(const void* p, int k0, int is_f32, bool take, float* f) {
+  if (!take) {
+#pragma unroll
+    for (int t = 0; t < 8; ++t) f[t] = 0.f;
+  } else if (is_f32) {
+    const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + k0);
+    const float4 c = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + k0 + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = c.x; f[5] = c.y; f[6] = c.z; f[7] = c.w;
+  } else {
+    const uint4 q = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p) + k0);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float2 v = __bfloat1622float2(h[t]);
+      f[2 * t] = v.x;
+      f[2 * t + 1] = v.y;
+    }
+  }
+}
+
 // The same for narrow rows: one warp per row, the row in registers (NI chunks of 8 per
 // lane, so widths up to NI * 256), sums met by shuffles only.  Gain and bias are parameters, not the
 // previous kernel's work: they are fetched before the dependent-launch wait.
@@ -106,11 +140,8 @@ layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ row_i
 #pragma unroll
   for (int i = 0; i < NI; ++i) {
     const int k0 = (lane + 32 * i) * 8;
-#pragma unroll
-    for (int t = 0; t < 8; ++t) {
-      g[i][t] = k0 < width ? load_param(gain, k0 + t, params_f32) : 0.f;
-      b[i][t] = (k0 < width && bias) ? load_param(bias, k0 + t, params_f32) : 0.f;
-    }
+    load_params8(gain, k0, params_f32, k0 < width, g[i]);
+    load_params8(bias, k0, params_f32, k0 < width && bias != nullptr, b[i]);
   }
   pdl_wait();
   if (r >= n_rows) return;
@@ -148,8 +179,10 @@ layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ row_i
   for (int i = 0; i < NI; ++i) {
     const int k0 = (lane + 32 * i) * 8;
     if (k0 < width) {
+      float y[8];
 #pragma unroll
-      for (int t = 0; t < 8; ++t) o[k0 + t] = from_f32<T>((v[i][t] - mean) * inv * g[i][t] + b[i][t]);
+      for (int t = 0; t < 8; ++t) y[t] = (v[i][t] - mean) * inv * g[i][t] + b[i][t];
+      store8(o + k0, y);
     }
   }
 }
@@ -160,7 +193,9 @@ KVAD_EXPORT int kvad_layernorm(int out_dtype, const float* x, const int* row_ind
   KVAD_REQUIRE(n_rows >= 0 && width > 0, "layernorm: bad sizes rows=%d width=%d", n_rows, width);
   KVAD_REQUIRE(gain != nullptr, "layernorm: no gain");
   if (n_rows == 0) return KVAD_OK;
-  if (width % 8 == 0 && width <= 1024 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+  if (width % 8 == 0 && width <= 1024 &&
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(gain) | reinterpret_cast<uintptr_t>(bias) |
+        reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
     // narrow rows: a warp per row
     const dim3 grid((n_rows + 3) / 4), block(128);
     if (out_dtype == KVAD_DTYPE_F32)

@@ -56,6 +56,8 @@ class _SampleBuffers:
         self.dev = torch.zeros((4, cap), dtype=torch.float32, device=device)
         self.out = torch.zeros(cap, dtype=torch.int32, device=device)
         self.out_host = torch.zeros(cap, dtype=torch.int32).pin_memory()
+        self.out_hosts = [torch.zeros(cap, dtype=torch.int32).pin_memory() for _ in range(2)]   # for reads that lag a step
+        self._parity = 0
         self.scratch = None                    # of the two-stage argmax
 
     def load(self, samplers, engine) -> bool:
@@ -73,11 +75,33 @@ class _SampleBuffers:
         engine.h2d_bytes += self.host.numel() * 4
         return False
 
+    def read_async(self, n: int, engine) -> "_PendingTokens":
+        """Starts the copy of the chosen tokens to the host and returns a handle; two host buffers
+        alternate, so a step launched ahead does not overwrite what the host has yet to read."""
+        host = self.out_hosts[self._parity]
+        self._parity ^= 1
+        host[:n].copy_(self.out[:n], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return _PendingTokens(host, n, event, engine)
+
     def read(self, n: int, engine) -> list[int]:
         self.out_host[:n].copy_(self.out[:n], non_blocking=True)
         torch.cuda.current_stream().synchronize()
         engine.d2h_bytes += 4 * n
         return self.out_host[:n].tolist()
+
+
+class _PendingTokens:
+    """Chosen tokens of a launched step, on their way to the host."""
+
+    def __init__(self, host: torch.Tensor, n: int, event, engine):
+        self.host, self.n, self.event, self.engine = host, n, event, engine
+
+    def tokens(self) -> list[int]:
+        self.event.synchronize()
+        self.engine.d2h_bytes += 4 * self.n
+        return self.host[:self.n].tolist()
 
 
 class _DecodePlan:
@@ -303,6 +327,14 @@ class Engine:
             return plan.bufs.read(len(entries), self)
         logits = self.step([StepEntry(slot, toks, (len(toks) - 1,)) for slot, toks in entries])
         return self.sample(logits, samplers)
+
+    def launch_step(self, entries, samplers, device_fed: bool = False) -> _PendingTokens:
+        """One token per sequence, launched and not waited for.  `entries`: [(slot, [token])], or
+        [(slot, None)] with `device_fed`: the tokens are the ones the step before chose for the same
+        sequences in the same order, still on the device.  Returns a handle whose `tokens()` waits."""
+        ents = [(slot, toks if toks is not None else [0]) for slot, toks in entries]
+        plan = self._decode(ents, samplers, device_fed=device_fed)
+        return plan.bufs.read_async(len(ents), self)
 
     # -- decoding through a captured graph -----------------------------------------------
     def _decode(self, entries, samplers, *, device_fed: bool = False) -> "_DecodePlan":

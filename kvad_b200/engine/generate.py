@@ -61,10 +61,46 @@ class Backend(Protocol):
     def step_and_sample(self, entries, samplers) -> list: ...
 
 
+def _apply(requests, live, chosen, backend, opened, stats, on_token, only=None):
+    """The loop's decisions for one step's chosen tokens; returns the items that go on.
+    `only`: if given, items outside it are skipped (they ended a step earlier)."""
+    still = []
+    for it, tok in zip(live, chosen):
+        if only is not None and not any(it is o for o in only):
+            continue
+        r = requests[it[0]]
+        tok = int(tok)
+        if tok in r.stop_token_ids:
+            r.finish_reason = "stop"          # not kept, not fed
+        else:
+            r.generated.append(tok)
+            stats.generated_tokens += 1
+            if on_token is not None:
+                on_token(it[0], tok)
+            it[3] -= 1
+            if it[3] == 0:
+                r.finish_reason = "length" if len(r.generated) >= r.max_tokens else "context"
+        if r.finish_reason is None:
+            it[4] = [tok]                      # fed in the next step
+            still.append(it)
+        else:
+            backend.close(it[1])               # leaves the batch at once
+            opened.remove(it[1])
+    return still
+
+
 def run_batch(backend: Backend, requests: Sequence[Request], stats: Optional[Stats] = None,
               on_token: Optional[Callable[[int, int], None]] = None,
               clock: Callable[[], float] = time.perf_counter) -> None:
-    """Runs one batch to its end.  Fills `generated` and `finish_reason` of every request."""
+    """Runs one batch to its end.  Fills `generated` and `finish_reason` of every request.
+
+    A backend that also offers `launch_step(entries, samplers, device_fed) -> handle` (with
+    `handle.tokens()`) is driven one step ahead: while the host waits for a step's tokens and
+    decides, the next step - fed on the device with those very tokens - is already running.  It is
+    launched only when no request can end by its budget in the step before; if a request ends by a
+    stop token, the step that ran ahead is still right for the others (sequences do not see one
+    another) and is merely wasted for the one that ended.  The decisions and the tokens are the same
+    either way."""
     stats = stats if stats is not None else Stats()
     live = []                     # [index, slot, sampler, left, pending tokens]
     for i, r in enumerate(requests):
@@ -78,44 +114,52 @@ def run_batch(backend: Backend, requests: Sequence[Request], stats: Optional[Sta
             continue
         live.append([i, None, RequestSampler(r.params, r.seed), left, list(r.prompt)])
     opened = []
+    pipelined = hasattr(backend, "launch_step")
     try:
         for item in live:
             item[1] = backend.open()
             opened.append(item[1])
         stats.batches += 1
-        first = True
-        while live:
-            t0 = clock()
-            chosen = backend.step_and_sample([(it[1], it[4]) for it in live], [it[2] for it in live])
-            dt = clock() - t0
-            stats.steps += 1
-            if first:
-                stats.prefill_secs += dt
-                stats.prompt_tokens += sum(len(it[4]) for it in live)
-                first = False
+        if not live:
+            return
+        # the prompts, in one step
+        t0 = clock()
+        chosen = backend.step_and_sample([(it[1], it[4]) for it in live], [it[2] for it in live])
+        stats.prefill_secs += clock() - t0
+        stats.steps += 1
+        stats.prompt_tokens += sum(len(it[4]) for it in live)
+        live = _apply(requests, live, chosen, backend, opened, stats, on_token)
+        # then one token each
+        t0 = clock()
+        try:
+            if not pipelined:
+                while live:
+                    chosen = backend.step_and_sample([(it[1], it[4]) for it in live], [it[2] for it in live])
+                    stats.steps += 1
+                    live = _apply(requests, live, chosen, backend, opened, stats, on_token)
             else:
-                stats.decode_secs += dt
-            still = []
-            for it, tok in zip(live, chosen):
-                r = requests[it[0]]
-                tok = int(tok)
-                if tok in r.stop_token_ids:
-                    r.finish_reason = "stop"          # not kept, not fed
-                else:
-                    r.generated.append(tok)
-                    stats.generated_tokens += 1
-                    if on_token is not None:
-                        on_token(it[0], tok)
-                    it[3] -= 1
-                    if it[3] == 0:
-                        r.finish_reason = "length" if len(r.generated) >= r.max_tokens else "context"
-                if r.finish_reason is None:
-                    it[4] = [tok]                      # fed in the next step
-                    still.append(it)
-                else:
-                    backend.close(it[1])               # leaves the batch at once
-                    opened.remove(it[1])
-            live = still
+                in_flight = None
+                while live:
+                    samplers = [it[2] for it in live]
+                    if in_flight is None:
+                        in_flight = backend.launch_step([(it[1], it[4]) for it in live], samplers, False)
+                    ahead = None
+                    if all(it[3] >= 2 for it in live):           # nobody can end by budget in the step in flight
+                        ahead = backend.launch_step([(it[1], None) for it in live], samplers, True)
+                    chosen = in_flight.tokens()
+                    stats.steps += 1
+                    still = _apply(requests, live, chosen, backend, opened, stats, on_token)
+                    if len(still) == len(live):
+                        in_flight = ahead
+                    else:
+                        if ahead is not None:                     # ran with the old company: right for those who go on
+                            chosen = ahead.tokens()
+                            stats.steps += 1
+                            still = _apply(requests, live, chosen, backend, opened, stats, on_token, only=still)
+                        in_flight = None
+                    live = still
+        finally:
+            stats.decode_secs += clock() - t0
     finally:
         for slot in opened:
             backend.close(slot)

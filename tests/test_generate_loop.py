@@ -135,3 +135,60 @@ def test_stats_and_on_token():
     run_batch(b, [greedy([1, 2], 2), greedy([5], 3)], stats, on_token=lambda i, t: seen.append((i, t)))
     assert stats.prompt_tokens == 3 and stats.generated_tokens == 5 and stats.steps == 3
     assert seen == [(0, 3), (1, 6), (0, 4), (1, 7), (1, 8)]
+
+
+class ScriptedAhead(Scripted):
+    """The same fake model with `launch_step`: steps are launched ahead and their tokens read later."""
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.last = {}             # slot -> the token its latest step chose (what a device-fed step continues from)
+        self.launched_ahead = 0
+
+    def step_and_sample(self, entries, samplers):
+        out = super().step_and_sample(entries, samplers)
+        for (slot, _), tok in zip(entries, out):
+            self.last[slot] = tok
+        return out
+
+    def launch_step(self, entries, samplers, device_fed):
+        if device_fed:
+            self.launched_ahead += 1
+            assert all(t is None for _, t in entries)
+            entries = [(slot, [self.last[slot]]) for slot, _ in entries]
+        else:
+            assert all(t == [self.last[slot]] for slot, t in entries), "host-fed tokens must be the ones chosen"
+        live = [s for s, _ in entries if s in self.open_slots]
+        out = []
+        self.calls.append([(s, list(t)) for s, t in entries])
+        for (slot, toks), smp in zip(entries, samplers):
+            self.held[slot] = self.held.get(slot, 0) + 1 if slot in self.held else 1
+            smp.next_uniform()
+            tok = (toks[-1] + 1) % 50
+            self.last[slot] = tok
+            out.append(tok)
+
+        class Handle:
+            def tokens(_self):
+                return out
+        return Handle()
+
+
+@pytest.mark.parametrize("case", [
+    [([1, 2, 3], 3, ()), ([10], 3, ())],
+    [([1], 10, (4,)), ([20], 5, ())],
+    [([1], 10, (3,)), ([20], 9, (24,)), ([30, 31], 6, ())],
+    [([5], 1, ()), ([6], 2, ()), ([7], 7, (9,))],
+])
+def test_running_a_step_ahead_changes_no_decision(case):
+    def run(backend):
+        reqs = [greedy(p, n, stop) for p, n, stop in case]
+        stats = Stats()
+        run_batch(backend, reqs, stats)
+        assert not backend.open_slots
+        return [(r.generated, r.finish_reason) for r in reqs], stats.generated_tokens
+
+    plain, ahead = Scripted(context=64), ScriptedAhead(context=64)
+    assert run(plain) == run(ahead)
+    if case[0][0] != [5]:              # (in the last case a request can end by its budget in every step)
+        assert ahead.launched_ahead > 0

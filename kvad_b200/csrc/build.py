@@ -28,7 +28,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
           "-shared", "-Xcompiler", "-fPIC"]
 #: every kernel library of the package, in the order `build_all` compiles them
-LIBRARIES = ("rows", "linear_simt", "attention_simt", "sampling", "linear_tcgen05",
+LIBRARIES = ("rows", "linear_simt", "attention_simt", "sampling", "linear_tcgen05", "linear_rows",
              "attention_prefill", "attention_decode")
 
 _loaded: dict[str, ctypes.CDLL] = {}

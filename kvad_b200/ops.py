@@ -56,6 +56,10 @@ _SIGNATURES = {
         "kvad_linear_tcgen05_ln": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p,
                                    c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p],
     },
+    "linear_rows": {
+        "kvad_linear_rows": [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int,
+                             c_void_p],
+    },
     "attention_simt": {
         "kvad_attention_simt": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
@@ -111,6 +115,8 @@ def libraries_for(dtype: torch.dtype) -> list[str]:
     names = ["rows", "linear_simt", "attention_simt", "sampling"]
     if dtype == torch.bfloat16:
         names += [n for n in ("linear_tcgen05", "attention_prefill", "attention_decode") if n in build.sources()]
+        if os.environ.get("KVAD_ROWS_LINEAR", "0") == "1":
+            names.append("linear_rows")
     return names
 
 
@@ -157,6 +163,11 @@ class Ops:
         self.tensor_core_linear = dtype == torch.bfloat16 and "linear_tcgen05" in build.sources()
         self.tensor_core_prefill = dtype == torch.bfloat16 and "attention_prefill" in build.sources()
         self.fast_decode = dtype == torch.bfloat16 and "attention_decode" in build.sources()
+        # Up to 16 rows the product can also run as a stream of weights through registers on the CUDA cores
+        # (linear_rows.cu).  Measured on a B200 it beats the tensor-core kernel only at one or two rows
+        # (qkv at 1 row: 2.4 us against 3.9 us) and loses from 8 rows on (down-projection at 8 rows: 9.2 us
+        # against 2.8 us), so it is not the default; KVAD_ROWS_LINEAR=1 or form="rows" selects it.
+        self.rows_linear = dtype == torch.bfloat16 and os.environ.get("KVAD_ROWS_LINEAR", "0") == "1"
         # One kernel for `layernorm -> linear` (at most 16 rows).  Measured on a B200 it is SLOWER than the
         # pair under dependent launch (GPT-2 small, batch 8: 0.55 ms a step against 0.50 ms): the separate
         # norm already hides behind the product's weight fetch, while the fused kernel puts the norm on every
@@ -204,8 +215,9 @@ class Ops:
                form: str = "auto") -> None:
         """out = epilogue(a . weight^T + bias); weight is [out_features, in_features].
 
-        `tile`, `splits` and `form` ("wide", "swapped") fix the tensor-core kernel's tile width, K
-        split and operand roles (0 / "auto": its own choice)."""
+        `form`: "auto"; "rows" (at most 16 rows: weights streamed through registers on the CUDA cores);
+        "wide" / "swapped" (the tensor-core kernel's two operand roles).  `tile` and `splits` fix the
+        tensor-core kernel's tile width and K split (0: its own choice)."""
         _need_cuda(a, weight, bias, out)
         epi = EPILOGUES[epilogue]
         lda, ldo = _rows_view(a, "linear input"), _rows_view(out, "linear output")
@@ -225,11 +237,19 @@ class Ops:
             bias_f32 = 1 if bias.dtype == torch.float32 else 0
             if not bias_f32 and bias.dtype != torch.bfloat16:
                 raise KernelError(f"linear: bias must be float32 or bfloat16, not {bias.dtype}")
+        if (self.dtype == torch.bfloat16 and (form == "rows" or (self.rows_linear and form == "auto")) and m <= 16 and k <= 4096 and k % 8 == 0 and lda % 8 == 0
+                and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
+            h = lib("linear_rows")
+            _check(h.kvad_linear_rows(_ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k, epi,
+                                      _stream()), h)
+            return
+        if form == "rows":
+            raise KernelError("linear: the weight-streaming form takes bfloat16, at most 16 rows and K a multiple of 8 up to 4096")
         if self.tensor_core_linear and tcgen05_takes(a, weight, out, lda, ldo):
             h = lib("linear_tcgen05")
             _check(h.kvad_linear_tcgen05(_ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k,
                                          epi, (int(tile) & 0xffff) | ((int(splits) & 0xff) << 16)
-                                         | ({"auto": 0, "wide": 1, "swapped": 2}[form] << 24), _stream()), h)
+                                         | ({"auto": 0, "wide": 1, "swapped": 2}.get(form, 0) << 24), _stream()), h)
             return
         h = lib("linear_simt")
         _check(h.kvad_linear_simt(self.code, _ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k,

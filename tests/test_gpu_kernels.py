@@ -529,3 +529,17 @@ def test_layernorm_fused_into_the_product(m):
     assert not ops.ln_linear_takes(17, 768, "store") and not ops.ln_linear_takes(8, 768, "residual")
     assert not ops.ln_linear_takes(8, 2056, "store")
     assert tcgen05_wait_timeouts() == 0
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 7, 8, 13, 16])
+def test_linear_weight_streaming_form(m):
+    """At most 16 rows: a warp per output column, the column's weights held in registers."""
+    ops = Ops(torch.bfloat16)
+    g = torch.Generator().manual_seed(400 + m)
+    for n, k in [(768, 768), (1000, 96), (50, 320), (2304, 64), (777, 3072), (50257, 768), (333, 1600), (40, 4096), (9, 8)]:
+        for epi in ("store", "gelu_tanh", "gelu_erf", "residual", "store_f32"):
+            assert linear_case(ops, "bfloat16", m, n, k, epi, g, form="rows") < KTOL["bfloat16"], (m, n, k, epi)
+    assert linear_case(ops, "bfloat16", m, 333, 128, "store", g, bias=False, strided=True, form="rows") < KTOL["bfloat16"]
+    assert linear_case(ops, "bfloat16", m, 333, 128, "residual", g, bias_f32=True, form="rows") < KTOL["bfloat16"]
+    with pytest.raises(KernelError, match="at most 16 rows"):
+        linear_case(ops, "bfloat16", 17, 64, 64, "store", g, form="rows")

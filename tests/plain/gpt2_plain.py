@@ -110,7 +110,7 @@ class PlainGpt2:
         from math import erf
         return 0.5 * t * (1.0 + np.vectorize(erf)(t / math.sqrt(2.0)))
 
-    def attention(self, q, k, v, layer):
+    def attention(self, q, k, v, layer, window=None):
         """Per head: scores = q.k * 1/sqrt(head_dim) over positions <= own; softmax with the maximum
         subtracted; weighted sum of values (crates/llm/src/model/mod.rs:769-819,
         crates/llm/src/tensor.rs:297-308).  Query head h reads KV head h // group
@@ -123,6 +123,8 @@ class PlainGpt2:
             scale /= (layer + 1)
         out = np.zeros((T, self.H * self.hd))
         causal = np.tril(np.ones((T, T), dtype=bool))
+        if window:                                  # a row sees its latest `window` positions only (itself included)
+            causal &= ~np.tril(np.ones((T, T), dtype=bool), -int(window))
         for h in range(self.H):
             kv = h // group
             qh = q[:, h * self.hd:(h + 1) * self.hd]
@@ -136,15 +138,18 @@ class PlainGpt2:
             out[:, h * self.hd:(h + 1) * self.hd] = p @ vh
         return out
 
-    def block(self, x, i):
-        """x += Attn(LN1(x)); x += MLP(LN2(x))  (crates/llm/src/model/gpt2.rs:229-266)."""
+    def block(self, x, i, window=None, rotate=None):
+        """x += Attn(LN1(x)); x += MLP(LN2(x))  (crates/llm/src/model/gpt2.rs:229-266).
+        `window` and `rotate` (a function of (q, k) -> (q, k)) serve tests of toy variants."""
         w, r = self.w, self.r
         p = f"h.{i}."
         h = r(self.layer_norm(x, w[p + "ln_1.weight"], w[p + "ln_1.bias"]))
         qkv = r(self.linear(h, w[p + "attn.c_attn.weight"], w[p + "attn.c_attn.bias"]))
         qw, kw = self.H * self.hd, self.Hkv * self.hd
         q, k, v = qkv[:, :qw], qkv[:, qw:qw + kw], qkv[:, qw + kw:]
-        a = r(self.attention(q, k, v, i))
+        if rotate is not None:
+            q, k = rotate(q, k)
+        a = r(self.attention(q, k, v, i, window))
         x = x + self.linear(a, w[p + "attn.c_proj.weight"], w[p + "attn.c_proj.bias"])
         h = r(self.layer_norm(x, w[p + "ln_2.weight"], w[p + "ln_2.bias"]))
         hid = self.linear(h, w[p + "mlp.c_fc.weight"], w[p + "mlp.c_fc.bias"])

@@ -234,3 +234,141 @@ def test_run_order_names_a_block_twice_and_shares_a_cache(model_dirs, plains):
         from kvad_b200.models.plan import Model
         base = gpt2.plan(gpt2.read_config(JsonView(TINY["A"])))
         Model(ModelPlan(**{**base.__dict__, "order": (LayerCall(0, 0, writes_cache=False),)}))
+
+
+def test_layers_with_a_window_have_storage_of_their_own(model_dirs, plains):
+    """GPT-2's parts again, but every second layer sees only its latest 40 positions: two groups of cache
+    entries with storage of their own, pages of the windowed group handed back as they slide out of reach,
+    and the same logits as the plain implementation with the same windows - whole, token by token, and
+    with a prompt that continues cached positions."""
+    from kvad_b200.models import gpt2
+    from tests.conftest import TINY
+    WINDOW = 40
+
+    def plan(cfg):
+        base = gpt2.plan(cfg)
+        blocks = []
+        for i, b in enumerate(base.blocks):
+            if i % 2 == 0:
+                mixer = b.params["mixer"].with_params(window=WINDOW)
+                b = PartSpec(b.kind, {**b.params, "mixer": mixer})
+            blocks.append(b)
+        return ModelPlan(**{**base.__dict__, "arch_id": "gpt2_windowed", "blocks": tuple(blocks)})
+
+    register(Architecture("gpt2_windowed", ("gpt2_windowed",), "gpt2 parts, windows on even layers", gpt2.read_config, plan))
+    try:
+        import shutil, tempfile
+        for dtype in ("float32", "bfloat16"):
+            with tempfile.TemporaryDirectory() as d:
+                shutil.copy(os.path.join(model_dirs["B"], "model.safetensors"), d)
+                json.dump(dict(TINY["B"], model_type="gpt2_windowed"), open(os.path.join(d, "config.json"), "w"))
+                e = Engine.from_pretrained(d, dtype, max_tokens=1024)
+            layout = e.model.cache_layout
+            assert [g.entries for g in layout.groups] == [(0, 2), (1,)] and layout.groups[0].need.window == WINDOW
+            plain = plains("B", dtype)
+
+            def reference(tokens):
+                x = plain.embed(tokens)
+                for i in range(3):
+                    x = plain.block(x, i, window=WINDOW if i % 2 == 0 else None)
+                return plain.head(x)
+
+            tol = 5e-6 if dtype == "float32" else 8e-3
+            t = random_tokens(31, 230, 1000)
+            ref = reference(t)
+            s = e.open()
+            got = [e.step([StepEntry(s, t[:100], range(100))]).cpu().numpy(),
+                   e.step([StepEntry(s, t[100:190], range(90))]).cpu().numpy()]       # continues cached positions
+            for j in range(190, 230):
+                got.append(e.step([StepEntry(s, [t[j]], [0])]).cpu().numpy())
+            assert rel_err(np.concatenate(got), ref) < tol, dtype
+            # the windowed group has dropped the pages no later row can reach; the other group keeps all
+            windowed, full = e.cache.pages_of(s, 0), e.cache.pages_of(s, 1)
+            assert [p >= 0 for p in windowed] == [False, False, True, True] and all(p >= 0 for p in full)
+            e.close(s)
+            e.cache.book.check_all_free()
+    finally:
+        unregister("gpt2_windowed")
+
+
+def test_a_position_encoding_that_acts_inside_the_mixer(model_dirs, plains):
+    """A toy rotary encoding registered from here: no table at the embedding, queries and keys turned by their
+    rows' positions before the keys are cached.  The attention mixer calls `rotate`; nothing else changes."""
+    from kvad_b200.models import gpt2
+    from kvad_b200.parts import PositionEncoding
+    from tests.conftest import TINY
+    HD, THETA = 16, 100.0
+
+    def angles(positions):
+        inv = THETA ** (-np.arange(0, HD, 2) / HD)
+        return np.asarray(positions, dtype=np.float64)[:, None] * inv[None, :]
+
+    class Rotary(PositionEncoding):
+        def __init__(self, prefix, head_dim):
+            super().__init__(prefix)
+            self.head_dim = head_dim
+
+        def rotate(self, ctx, q, k):
+            pos = ctx.row_pos[:ctx.n_rows].double()
+            inv = torch.tensor(THETA ** (-np.arange(0, self.head_dim, 2) / self.head_dim), device=q.device)
+            ang = pos[:, None] * inv[None, :]
+            cos, sin = torch.cos(ang), torch.sin(ang)
+            for t in (q, k):
+                v = t.double().view(t.shape[0], -1, self.head_dim // 2, 2)
+                a, b = v[..., 0].clone(), v[..., 1].clone()
+                v[..., 0] = a * cos[:, None, :] - b * sin[:, None, :]
+                v[..., 1] = a * sin[:, None, :] + b * cos[:, None, :]
+                t.copy_(v.view(t.shape[0], -1).to(t.dtype))
+
+    def plan(cfg):
+        base = gpt2.plan(cfg)
+        blocks = [PartSpec(b.kind, {**b.params, "mixer": b.params["mixer"].with_params(position=PartSpec("toy_rotary", {"head_dim": HD}))})
+                  for b in base.blocks]
+        emb = PartSpec("token_embedding", {**base.embedding.params, "position": PartSpec("none", {})})
+        return ModelPlan(**{**base.__dict__, "arch_id": "gpt2_rotary", "blocks": tuple(blocks), "embedding": emb})
+
+    register_part("position", "toy_rotary", Rotary)
+    register(Architecture("gpt2_rotary", ("gpt2_rotary",), "gpt2 parts, toy rotary positions", gpt2.read_config, plan))
+    try:
+        import shutil, tempfile
+        with tempfile.TemporaryDirectory() as d:
+            shutil.copy(os.path.join(model_dirs["A"], "model.safetensors"), d)
+            json.dump(dict(TINY["A"], model_type="gpt2_rotary"), open(os.path.join(d, "config.json"), "w"))
+            from kvad_b200.weights import Checkpoint
+            ck = Checkpoint([os.path.join(d, "model.safetensors")])
+            tensors = {n: ck.read(n) for n in ck.names() if n != "wpe.weight"}      # no position table in this model
+            ck.close()
+            write_safetensors(os.path.join(d, "model.safetensors"), tensors)
+            e = Engine.from_pretrained(d, "float32", max_tokens=512)
+        assert e.max_positions is None and not e.use_graphs
+        plain = plains("A")
+
+        def reference(tokens):
+            ang = angles(range(len(tokens)))
+            cos, sin = np.cos(ang), np.sin(ang)
+
+            def rot(q, k):
+                out = []
+                for t in (q, k):
+                    v = t.reshape(t.shape[0], -1, HD // 2, 2).copy()
+                    a, b = v[..., 0].copy(), v[..., 1].copy()
+                    v[..., 0] = a * cos[:, None, :] - b * sin[:, None, :]
+                    v[..., 1] = a * sin[:, None, :] + b * cos[:, None, :]
+                    out.append(v.reshape(t.shape[0], -1))
+                return out
+            x = plain.w["wte.weight"][np.asarray(tokens)]
+            for i in range(2):
+                x = plain.block(x, i, rotate=rot)
+            return plain.head(x)
+
+        t = random_tokens(41, 150, 512)                    # beyond the 128 positions the learned table had
+        ref = reference(t)
+        s = e.open()
+        got = [e.step([StepEntry(s, t[:140], range(140))]).cpu().numpy()]
+        for j in range(140, 150):
+            got.append(e.step([StepEntry(s, [t[j]], [0])]).cpu().numpy())
+        e.close(s)
+        assert rel_err(np.concatenate(got), ref) < 1e-5
+    finally:
+        unregister("gpt2_rotary")
+        unregister_part("position", "toy_rotary")

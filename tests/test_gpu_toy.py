@@ -372,3 +372,94 @@ def test_a_position_encoding_that_acts_inside_the_mixer(model_dirs, plains):
     finally:
         unregister("gpt2_rotary")
         unregister_part("position", "toy_rotary")
+
+
+def test_a_feed_forward_with_routing(model_dirs, plains):
+    """A toy feed-forward with two experts and a router, registered from here: every row goes to the expert
+    its 32-bit router logit prefers, the expert's output is scaled by the router's probability.  It replaces
+    the dense MLP in one of the two layers; mixers, norms, cache and the step function are untouched."""
+    from kvad_b200.models import gpt2
+    from kvad_b200.parts import FeedForward
+    from tests.conftest import TINY
+    E, HID = 64, 48
+
+    class RoutedFF(FeedForward):
+        def __init__(self, prefix, width, hidden, n_experts):
+            super().__init__(prefix)
+            self.width, self.hidden, self.n = width, hidden, n_experts
+            self.router = Linear(prefix + "router.", width, n_experts, bias=False)
+            self.up = [Linear(f"{prefix}experts.{i}.up.", width, hidden) for i in range(n_experts)]
+            self.down = [Linear(f"{prefix}experts.{i}.down.", hidden, width) for i in range(n_experts)]
+
+        def children(self):
+            return [self.router, *self.up, *self.down]
+
+        def forward(self, ctx, h, residual):
+            hf = h.float()
+            logits = hf @ self.router.weight.float().t()                       # router logits in 32-bit
+            prob, pick = torch.softmax(logits, -1).max(-1)
+            for i in range(self.n):
+                rows = (pick == i).nonzero().flatten()
+                if rows.numel():
+                    hid = torch.nn.functional.gelu(hf[rows] @ self.up[i].weight.float().t() + self.up[i].bias.float(), approximate="tanh")
+                    out = hid @ self.down[i].weight.float().t() + self.down[i].bias.float()
+                    residual.index_add_(0, rows, out * prob[rows, None])
+
+    def plan(cfg):
+        base = gpt2.plan(cfg)
+        routed = PartSpec("toy_routed", {"width": E, "hidden": HID, "n_experts": 2})
+        blocks = [base.blocks[0], PartSpec("pre_norm", {**base.blocks[1].params, "feed_forward": routed})]
+        return ModelPlan(**{**base.__dict__, "arch_id": "gpt2_routed", "blocks": tuple(blocks)})
+
+    register_part("feed_forward", "toy_routed", RoutedFF)
+    register(Architecture("gpt2_routed", ("gpt2_routed",), "gpt2 parts, a routed feed-forward in layer 1", gpt2.read_config, plan))
+    try:
+        import tempfile
+        from kvad_b200.weights import Checkpoint
+        g = torch.Generator().manual_seed(3)
+        with tempfile.TemporaryDirectory() as d:
+            ck = Checkpoint([os.path.join(model_dirs["A"], "model.safetensors")])
+            tensors = {n: ck.read(n).float() for n in ck.names() if not n.startswith("h.1.mlp.c_")}
+            ck.close()
+            extra = {"h.1.mlp.router.weight": torch.randn(2, E, generator=g)}
+            for i in range(2):
+                extra[f"h.1.mlp.experts.{i}.up.weight"] = torch.randn(HID, E, generator=g) * 0.2
+                extra[f"h.1.mlp.experts.{i}.up.bias"] = torch.randn(HID, generator=g) * 0.1
+                extra[f"h.1.mlp.experts.{i}.down.weight"] = torch.randn(E, HID, generator=g) * 0.2
+                extra[f"h.1.mlp.experts.{i}.down.bias"] = torch.randn(E, generator=g) * 0.1
+            write_safetensors(os.path.join(d, "model.safetensors"), {**tensors, **extra})
+            json.dump(dict(TINY["A"], model_type="gpt2_routed"), open(os.path.join(d, "config.json"), "w"))
+            e = Engine.from_pretrained(d, "float32", max_tokens=512)
+        plain = plains("A")
+        x64 = {k: v.double().numpy() for k, v in extra.items()}
+
+        def reference(tokens):
+            w = plain.w
+            x = plain.block(plain.embed(tokens), 0)
+            # layer 1: GPT-2's attention half, then the routed feed-forward
+            h = plain.layer_norm(x, w["h.1.ln_1.weight"], w["h.1.ln_1.bias"])
+            qkv = plain.linear(h, w["h.1.attn.c_attn.weight"], w["h.1.attn.c_attn.bias"])
+            a = plain.attention(qkv[:, :64], qkv[:, 64:128], qkv[:, 128:], 1)
+            x = x + plain.linear(a, w["h.1.attn.c_proj.weight"], w["h.1.attn.c_proj.bias"])
+            h = plain.layer_norm(x, w["h.1.ln_2.weight"], w["h.1.ln_2.bias"])
+            logits = h @ x64["h.1.mlp.router.weight"].T
+            p = np.exp(logits - logits.max(-1, keepdims=True))
+            p /= p.sum(-1, keepdims=True)
+            pick = p.argmax(-1)
+            for r in range(len(tokens)):
+                i = pick[r]
+                hid = plain.gelu_tanh(h[r] @ x64[f"h.1.mlp.experts.{i}.up.weight"].T + x64[f"h.1.mlp.experts.{i}.up.bias"])
+                x[r] = x[r] + (hid @ x64[f"h.1.mlp.experts.{i}.down.weight"].T + x64[f"h.1.mlp.experts.{i}.down.bias"]) * p[r, i]
+            return plain.head(x)
+
+        t = random_tokens(51, 60, 512)
+        ref = reference(t)
+        s = e.open()
+        got = [e.step([StepEntry(s, t[:50], range(50))]).cpu().numpy()]
+        for j in range(50, 60):
+            got.append(e.step([StepEntry(s, [t[j]], [0])]).cpu().numpy())
+        e.close(s)
+        assert rel_err(np.concatenate(got), ref) < 1e-5
+    finally:
+        unregister("gpt2_routed")
+        unregister_part("feed_forward", "toy_routed")

@@ -271,6 +271,7 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ scratch,
 // one, so their first stages are requested before the dependent-launch wait.
 // Every wait is bounded; one that runs out raises g_decode_timeouts and the CTA runs on to its end.
 // ---------------------------------------------------------------------------------------------
+bool g_no_cluster = false;       // tests: merge the splits through global memory even where a cluster could
 bool g_force_plain = false;      // tests: keep every head size on the kernel that loads through registers
 constexpr int TMA_CONSUMER_WARPS = 4;
 constexpr int TMA_THREADS = (TMA_CONSUMER_WARPS + 1) * 32;
@@ -322,7 +323,7 @@ attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict
                             T* __restrict__ k_pages, T* __restrict__ v_pages,
                             const T* __restrict__ k_new, const T* __restrict__ v_new, int64_t ld_new,
                             float* __restrict__ scratch, int* __restrict__ counters,
-                            int n_heads, int n_kv_heads, int n_splits, float scale, int window) {
+                            int n_heads, int n_kv_heads, int n_splits, float scale, int window, int cluster_merge) {
   using D = DecTile<T, HD>;
   constexpr int STAGES = D::STAGES;
   constexpr int CH = HD / 8;                       // lanes per key
@@ -492,6 +493,42 @@ attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict
     wscale[w] = (ml_sh[w][0] == -INFINITY) ? 0.f : exp_for<T>(ml_sh[w][0] - m);
     total += ml_sh[w][1] * wscale[w];
   }
+  if (n_splits > 1 && cluster_merge) {
+    // The splits of this (row, head) are the CTAs of one thread-block cluster: each leaves its partial in
+    // its own shared memory, the cluster meets, and the first CTA reads the others' through distributed
+    // shared memory.  No trip to global memory, no fence, no counter.
+    __shared__ float part_sh[HD + 2];
+    for (int d = tid; d < HD; d += TMA_THREADS) {
+      float o = 0.f;
+#pragma unroll
+      for (int w = 0; w < TMA_CONSUMER_WARPS; ++w) o += acc_sh[w][d] * wscale[w];
+      part_sh[d] = o;
+    }
+    if (tid == 0) {
+      part_sh[HD] = m;
+      part_sh[HD + 1] = total;
+    }
+    cluster_sync_all();
+    if (split == 0) {
+      float gm = -INFINITY;
+      for (int s2 = 0; s2 < n_splits; ++s2) gm = fmaxf(gm, ld_cluster_f32(&part_sh[HD], (unsigned)s2));
+      float gl = 0.f;
+      for (int s2 = 0; s2 < n_splits; ++s2) {
+        const float ms = ld_cluster_f32(&part_sh[HD], (unsigned)s2);
+        if (ms != -INFINITY) gl += ld_cluster_f32(&part_sh[HD + 1], (unsigned)s2) * exp_for<T>(ms - gm);
+      }
+      for (int d = tid; d < HD; d += TMA_THREADS) {
+        float o = 0.f;
+        for (int s2 = 0; s2 < n_splits; ++s2) {
+          const float ms = ld_cluster_f32(&part_sh[HD], (unsigned)s2);
+          if (ms != -INFINITY) o += ld_cluster_f32(&part_sh[d], (unsigned)s2) * exp_for<T>(ms - gm);
+        }
+        out[(int64_t)r * ld_out + (int64_t)h * HD + d] = from_f32<T>(o / gl);
+      }
+    }
+    cluster_sync_all();          // nobody's shared memory goes away while the first CTA reads it
+    return;
+  }
   float* part = n_splits > 1 ? scratch + (((int64_t)r * n_heads + h) * n_splits + split) * (HD + 2) : nullptr;
   for (int d = tid; d < HD; d += TMA_THREADS) {
     float o = 0.f;
@@ -539,10 +576,19 @@ int launch(const void* q, int64_t ld_q, void* out, int64_t ld_out, const int* ro
       if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "attention_decode: cannot reserve %zu bytes of shared memory: %s", D::SMEM, cudaGetErrorString(e));
       configured = true;
     }
-    kvad_launch(attention_decode_tma_kernel<T, HD>, grid, dim3(TMA_THREADS), D::SMEM, stream,
-        (const T*)q, ld_q, (T*)out, ld_out, row_seq, row_pos, page_table, table_width, (T*)const_cast<void*>(k_pages),
-        (T*)const_cast<void*>(v_pages), (const T*)k_new, (const T*)v_new, ld_new, scratch, counters, n_heads, n_kv_heads,
-        n_splits, scale, window);
+    // with 2..8 splits and a merge asked for in the kernel, the splits form a cluster and merge on chip
+    const bool cluster = counters != nullptr && n_splits > 1 && n_splits <= 8 && !g_no_cluster;
+    if (cluster) {
+      kvad_launch_cluster(attention_decode_tma_kernel<T, HD>, grid, dim3(TMA_THREADS), D::SMEM, stream, n_splits,
+          (const T*)q, ld_q, (T*)out, ld_out, row_seq, row_pos, page_table, table_width, (T*)const_cast<void*>(k_pages),
+          (T*)const_cast<void*>(v_pages), (const T*)k_new, (const T*)v_new, ld_new, scratch, counters, n_heads, n_kv_heads,
+          n_splits, scale, window, 1);
+    } else {
+      kvad_launch(attention_decode_tma_kernel<T, HD>, grid, dim3(TMA_THREADS), D::SMEM, stream,
+          (const T*)q, ld_q, (T*)out, ld_out, row_seq, row_pos, page_table, table_width, (T*)const_cast<void*>(k_pages),
+          (T*)const_cast<void*>(v_pages), (const T*)k_new, (const T*)v_new, ld_new, scratch, counters, n_heads, n_kv_heads,
+          n_splits, scale, window, 0);
+    }
   } else {
     kvad_launch(attention_decode_kernel<T, HD>, grid, dim3(DEC_THREADS), 0, stream,
         (const T*)q, ld_q, (T*)out, ld_out, row_seq, row_pos, page_table, table_width, (T*)const_cast<void*>(k_pages),
@@ -559,9 +605,9 @@ int launch(const void* q, int64_t ld_q, void* out, int64_t ld_out, const int* ro
 
 }  // namespace
 
-// Tests: 1 keeps every head size on the kernel that loads through registers; 0 lets the head sizes
-// 16, 32, 64, 128 and 256 take the TMA-fed kernel.
-KVAD_EXPORT void kvad_attention_decode_force_plain(int on) { g_force_plain = on != 0; }
+// Tests: 1 keeps every head size on the kernel that loads through registers; 2 keeps the TMA-fed kernel
+// but merges its splits through global memory instead of a cluster's shared memory; 0: the kernel's own choice.
+KVAD_EXPORT void kvad_attention_decode_force_plain(int on) { g_force_plain = on == 1; g_no_cluster = on == 2; }
 
 // How many bounded waits of the TMA-fed kernel have run out (0 in a healthy run).  Synchronises the device.
 KVAD_EXPORT int kvad_attention_decode_status() {

@@ -355,7 +355,7 @@ class Ops:
         """Into how many key ranges a decode step cuts each (row, head): enough CTAs to fill the GPU
         twice over, at most one range per page.  Depends on the batch's size only, never on lengths."""
         want = -(-2 * 148 // max(1, n_rows * n_heads))
-        return max(1, min(want, table_width, 32))
+        return max(1, min(want, table_width, 8))          # at most 8: the splits of a row and head form one cluster
 
     def attention_decode(self, q, out, row_seq, row_pos, page_table, k_pages, v_pages, n_heads: int, scale: float,
                          window: int = 0, *, n_splits: int = 1, scratch=None, k_new=None, v_new=None,
@@ -432,12 +432,13 @@ class Ops:
                              _ptr(uniform), _ptr(out), _stream()), h)
 
 
-def decode_force_plain(on: bool) -> None:
-    """Tests: keep the decode attention of every head size on the kernel that loads through registers."""
+def decode_force_plain(on) -> None:
+    """Tests: 1 / True keeps the decode attention of every head size on the kernel that loads through
+    registers; 2 keeps the TMA-fed kernel but merges splits through global memory, not a cluster; 0: default."""
     h = lib("attention_decode")
     h.kvad_attention_decode_force_plain.argtypes = [c_int]
     h.kvad_attention_decode_force_plain.restype = None
-    h.kvad_attention_decode_force_plain(int(bool(on)))
+    h.kvad_attention_decode_force_plain(int(on))
 
 
 def decode_wait_timeouts() -> int:

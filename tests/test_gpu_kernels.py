@@ -365,14 +365,14 @@ def test_argmax_first_of_equals_and_nan():
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("hd,n_heads,n_kv,window", [(16, 4, 4, 0), (48, 6, 2, 0), (64, 12, 12, 0), (80, 3, 1, 0),
                                                     (128, 2, 2, 50), (256, 2, 1, 0), (32, 5, 5, 64), (112, 2, 2, 0)])
-@pytest.mark.parametrize("form", ["tma", "registers"])
+@pytest.mark.parametrize("form", ["tma", "registers", "tma-no-cluster"])
 def test_attention_decode_split_keys(dtype, hd, n_heads, n_kv, window, form):
     """The decode kernel (both of its forms) at every split count gives what the plain reference gives; sequences
     of very unequal length share a launch (an empty split, a single key, a page boundary)."""
     from kvad_b200.ops import decode_force_plain, decode_wait_timeouts
     g = torch.Generator().manual_seed(7 * hd + n_heads)
     ops = Ops(DT[dtype])
-    decode_force_plain(form == "registers")
+    decode_force_plain({"tma": 0, "registers": 1, "tma-no-cluster": 2}[form])
     try:
         _decode_split_case(ops, g, dtype, hd, n_heads, n_kv, window)
     finally:
@@ -409,7 +409,7 @@ def _decode_split_case(ops, g, dtype, hd, n_heads, n_kv, window):
         kp2[table[s_, (l - 1) // 64], :, (l - 1) % 64] = float("nan")
         vp2[table[s_, (l - 1) // 64], :, (l - 1) % 64] = float("nan")
     new_d, kp_d, vp_d = dev(new), dev(kp2), dev(vp2)
-    for splits in (1, 3, 3, 16):
+    for splits in (1, 3, 3, 8, 16):
         out = torch.full((len(lens), n_heads * hd), float("nan"), device="cuda", dtype=DT[dtype])
         scratch = torch.full((len(lens) * n_heads * splits * (hd + 2),), float("nan"), device="cuda")
         ops.attention_decode(q_d, out, dev(row_seq), dev(row_pos), dev(table), kp_d, vp_d, n_heads, scale, window,

@@ -579,7 +579,7 @@ int launch(const void* q, int64_t ld_q, void* out, int64_t ld_out, const int* ro
     // with 2..8 splits and a merge asked for in the kernel, the splits form a cluster and merge on chip
     const bool cluster = counters != nullptr && n_splits > 1 && n_splits <= 8 && !g_no_cluster;
     if (cluster) {
-      kvad_launch_cluster(attention_decode_tma_kernel<T, HD>, grid, dim3(TMA_THREADS), D::SMEM, stream, n_splits,
+      kvad_launch_cluster(attention_decode_tma_kernel<T, HD>, grid, dim3(TMA_THREADS), D::SMEM, stream, dim3(n_splits, 1, 1),
           (const T*)q, ld_q, (T*)out, ld_out, row_seq, row_pos, page_table, table_width, (T*)const_cast<void*>(k_pages),
           (T*)const_cast<void*>(v_pages), (const T*)k_new, (const T*)v_new, ld_new, scratch, counters, n_heads, n_kv_heads,
           n_splits, scale, window, 1);

@@ -65,11 +65,11 @@ static inline cudaError_t kvad_launch(void (*kernel)(KArgs...), dim3 grid, dim3 
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
-// The same with the grid cut into thread-block clusters of `cluster_x` CTAs along x (at most 8): the CTAs
+// The same with the grid cut into thread-block clusters of `cluster` CTAs (at most 8 in all): the CTAs
 // of a cluster run together on one GPC and can read one another's shared memory.
 template <typename... KArgs, typename... Args>
 static inline cudaError_t kvad_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                              cudaStream_t stream, int cluster_x, Args... args) {
+                                              cudaStream_t stream, dim3 cluster, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -77,9 +77,9 @@ static inline cudaError_t kvad_launch_cluster(void (*kernel)(KArgs...), dim3 gri
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)cluster_x;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
+  attr[0].val.clusterDim.x = cluster.x;
+  attr[0].val.clusterDim.y = cluster.y;
+  attr[0].val.clusterDim.z = cluster.z;
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;

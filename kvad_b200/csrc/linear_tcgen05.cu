@@ -54,6 +54,7 @@ constexpr int SMEM_BUDGET_WIDE = 192 * 1024;     // the wide form keeps 33 KB fo
 
 __device__ int g_wait_timeouts = 0;
 bool g_no_3d = false;               // tests: keep the swapped form on one TMA load per K block
+bool g_no_cluster_k = false;        // tests: never split K over a cluster under a storing epilogue
 bool g_no_tma_out = false;          // tests: the wide form writes its output with plain stores
 bool g_force_3d = false;            // tests: take the grouped three-dimensional loads at every row count
 
@@ -579,7 +580,7 @@ template <int MB, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 linear_tcgen05_skinny3d_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                                const void* __restrict__ bias, int bias_f32, void* __restrict__ out, int64_t ldo,
-                               int M, int N, int K, int kb_per_split, int stages) {
+                               int M, int N, int K, int kb_per_split, int stages, int cluster_reduce) {
   constexpr uint32_t W_BYTES = BM * BK * 2;            // one K block of 128 weight rows
   constexpr uint32_t A_BYTES = MB * BK * 2;            // one K block of the activation rows
   constexpr int TMEM_COLS = MB < 32 ? 32 : MB;
@@ -592,6 +593,7 @@ linear_tcgen05_skinny3d_kernel(const __grid_constant__ CUtensorMap map_a, const 
   uint64_t* a_full = w_empty + stages;
   uint64_t* tmem_full_bar = a_full + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+  float* red_sh = reinterpret_cast<float*>(tmem_slot + 4);             // [MB][128]: this CTA's partial sums (cluster_reduce)
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -671,7 +673,17 @@ linear_tcgen05_skinny3d_kernel(const __grid_constant__ CUtensorMap map_a, const 
     pdl_wait();
     const bool ok = mbar_wait(tmem_full_bar, 0);
     tc_fence_after();
-    if (ok) {
+    if (ok && cluster_reduce) {
+      // K is split over the CTAs of a thread-block cluster: this CTA's partial sums go to its shared memory
+      const int n_local = quarter * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < MB; c += 16) {
+        float v[16];
+        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) red_sh[(c + j) * BM + n_local] = v[j];
+      }
+    } else if (ok) {
       const bool atomic = gridDim.y > 1;
 #pragma unroll 1
       for (int c = 0; c < MB; c += 16) {
@@ -701,6 +713,38 @@ linear_tcgen05_skinny3d_kernel(const __grid_constant__ CUtensorMap map_a, const 
     }
   }
 
+  if (cluster_reduce) {
+    // the cluster meets; its CTAs share the rows out, and each adds its rows' partial sums from all CTAs (its
+    // own included, in rank order) through distributed shared memory, applies bias and activation and stores;
+    // a second meeting keeps every CTA's memory alive until all have read it
+    __syncwarp();
+    cluster_sync_all();
+    if (warp >= 2) {
+      // row m is summed by CTA m % (cluster size): every CTA reads one row's partial sums from all of them
+      const int n_local = (warp & 3) * 32 + lane;
+      const int n = n0 + n_local;
+      const int z = (int)gridDim.y;
+      if (n < N) {
+        const float b = bias != nullptr ? load_param(bias, n, bias_f32) : 0.f;
+        for (int m = (int)blockIdx.y; m < M; m += z) {
+          float part[8];
+#pragma unroll
+          for (int rk = 0; rk < 8; ++rk) part[rk] = rk < z ? ld_cluster_f32(&red_sh[m * BM + n_local], (unsigned)rk) : 0.f;
+          float t = b;
+#pragma unroll
+          for (int rk = 0; rk < 8; ++rk) t += part[rk];
+          if (EPI == EPI_GELU_TANH) t = gelu_tanh_fast(t);
+          if (EPI == EPI_GELU_ERF) t = gelu_erf(t);
+          const int64_t o = (int64_t)m * ldo + n;
+          if (EPI == EPI_STORE_F32) reinterpret_cast<float*>(out)[o] = t;
+          else if (EPI == EPI_RESIDUAL) reinterpret_cast<float*>(out)[o] += t;
+          else reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(t);
+        }
+      }
+    }
+    __syncwarp();
+    cluster_sync_all();
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -1123,14 +1167,20 @@ int launch_skinny_epi(int epilogue, const CUtensorMap& ma, const CUtensorMap& mw
 template <int MB, int EPI>
 int launch_skinny3d(const CUtensorMap& ma, const CUtensorMap& mw, const void* bias, int bias_f32, void* out, int64_t ldo,
                     int M, int N, int K, int kb_per_split, int z, int stages, size_t smem, cudaStream_t stream) {
+  // a split of K under a storing epilogue is reduced inside a thread-block cluster (the residual epilogue adds atomically)
+  const int cluster_reduce = (EPI != EPI_RESIDUAL && z > 1) ? 1 : 0;
   static size_t configured = 0;
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(linear_tcgen05_skinny3d_kernel<MB, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "linear_tcgen05: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = smem;
   }
-  kvad_launch(linear_tcgen05_skinny3d_kernel<MB, EPI>, dim3((N + BM - 1) / BM, z), dim3(NUM_THREADS), smem, stream, ma, mw,
-              bias, bias_f32, out, ldo, M, N, K, kb_per_split, stages);
+  if (cluster_reduce)
+    kvad_launch_cluster(linear_tcgen05_skinny3d_kernel<MB, EPI>, dim3((N + BM - 1) / BM, z), dim3(NUM_THREADS), smem, stream,
+                        dim3(1, z, 1), ma, mw, bias, bias_f32, out, ldo, M, N, K, kb_per_split, stages, 1);
+  else
+    kvad_launch(linear_tcgen05_skinny3d_kernel<MB, EPI>, dim3((N + BM - 1) / BM, z), dim3(NUM_THREADS), smem, stream, ma, mw,
+                bias, bias_f32, out, ldo, M, N, K, kb_per_split, stages, 0);
   KVAD_CHECK_LAUNCH("linear_tcgen05_skinny3d");
   return KVAD_OK;
 }
@@ -1257,17 +1307,24 @@ KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, c
         if (sp3 > 16) sp3 = 16;
         if (sp3 > kb_all) sp3 = kb_all;
         if (sp3 < 1) sp3 = 1;
+      } else if (!g_no_cluster_k) {
+        // storing epilogues: K over a cluster of CTAs (8 at most) when that does not outnumber the SMs; measured
+        // at 8 rows and K = 768: 4.3 us whole, 4.3 in two, 3.8 in four, 3.8..4.1 in six
+        sp3 = force_splits > 0 ? force_splits : (kb_all >= 32 ? 8 : (kb_all >= 8 ? 4 : 1));
+        if (sp3 > 8) sp3 = 8;
+        if (sp3 > kb_all) sp3 = kb_all;
+        while (sp3 > 1 && tiles128 * sp3 > 160) --sp3;
       }
       const int kb_per_split = (kb_all + sp3 - 1) / sp3;
       const int z = (kb_all + kb_per_split - 1) / kb_per_split;
       const size_t a_bytes = (size_t)kb_per_split * mb * BK * 2;
       const size_t stage_bytes = (size_t)W_GROUP * BM * BK * 2;
       const int groups = (kb_per_split + W_GROUP - 1) / W_GROUP;
-      if (a_bytes + stage_bytes + 2048 <= (size_t)SMEM_BUDGET && kb_per_split <= 256) {
-        int stages3 = (int)(((size_t)SMEM_BUDGET - a_bytes - 2048) / stage_bytes);
+      if (a_bytes + stage_bytes + 2048 + (size_t)mb * BM * 4 <= (size_t)SMEM_BUDGET && kb_per_split <= 256) {
+        int stages3 = (int)(((size_t)SMEM_BUDGET - a_bytes - 2048 - (size_t)mb * BM * 4) / stage_bytes);
         if (stages3 > groups) stages3 = groups;
         if (stages3 > 3) stages3 = 3;
-        const size_t smem3 = a_bytes + (size_t)stages3 * stage_bytes + (2 * stages3 + 2) * 8 + 16 + 1024;
+        const size_t smem3 = a_bytes + (size_t)stages3 * stage_bytes + (2 * stages3 + 2) * 8 + 16 + 16 + (size_t)mb * BM * 4 + 1024;
         CUtensorMap ma3, mw3;
         int rc3 = tensor_map_3d(A, lda, M, K, mb, kb_per_split, &ma3);
         if (rc3 != KVAD_OK) return rc3;
@@ -1349,6 +1406,9 @@ KVAD_EXPORT void kvad_linear_tcgen05_no_3d(int on) { g_no_3d = on == 1; g_force_
 
 // Tests: 1 makes the wide form write its output with plain stores instead of TMA stores / reduce-adds.
 KVAD_EXPORT void kvad_linear_tcgen05_no_tma_out(int on) { g_no_tma_out = on != 0; }
+
+// Tests: 1 keeps K whole under the storing epilogues of the swapped form (no cluster reduction).
+KVAD_EXPORT void kvad_linear_tcgen05_no_cluster_k(int on) { g_no_cluster_k = on != 0; }
 
 // How many bounded waits have run out since the library was loaded (0 in a healthy run).
 // Synchronises the device.

@@ -461,6 +461,14 @@ def tcgen05_load_form(mode: int) -> None:
     h.kvad_linear_tcgen05_no_3d(int(mode))
 
 
+def tcgen05_cluster_k(on: bool) -> None:
+    """Tests: False keeps K whole under the storing epilogues of the swapped form (no reduction inside a cluster)."""
+    h = build.load("linear_tcgen05")
+    h.kvad_linear_tcgen05_no_cluster_k.argtypes = [c_int]
+    h.kvad_linear_tcgen05_no_cluster_k.restype = None
+    h.kvad_linear_tcgen05_no_cluster_k(int(not on))
+
+
 def tcgen05_plain_stores(on: bool) -> None:
     """Tests: the wide linear kernel writes its output with plain stores instead of TMA stores / reduce-adds."""
     h = lib("linear_tcgen05")

@@ -182,7 +182,7 @@ def test_linear_tensor_cores_swapped_form(m):
     ops = Ops(torch.bfloat16)
     if not ops.tensor_core_linear:
         pytest.skip("tensor-core linear kernel not built")
-    from kvad_b200.ops import tcgen05_load_form, tcgen05_wait_timeouts
+    from kvad_b200.ops import tcgen05_cluster_k, tcgen05_load_form, tcgen05_wait_timeouts
     g = torch.Generator().manual_seed(70 + m)
     for n, k in [(768, 768), (1000, 96), (50, 320), (2304, 64), (777, 3072), (50257, 768)]:
         for epi in ("store", "gelu_tanh", "gelu_erf", "residual", "store_f32"):
@@ -196,6 +196,15 @@ def test_linear_tensor_cores_swapped_form(m):
                 assert linear_case(ops, "bfloat16", m, n, k, epi, g, form="swapped", tile=tile) < KTOL["bfloat16"], (m, n, k, epi, tile)
         for splits in (1, 2, 5, 16):
             assert linear_case(ops, "bfloat16", m, n, k, "residual", g, form="swapped", splits=splits) < KTOL["bfloat16"]
+        # storing epilogues: K over the CTAs of a cluster (1, 2, 4 or 8 of them), and kept whole
+        for epi in ("store", "gelu_tanh", "store_f32"):
+            for splits in (2, 4, 8):
+                assert linear_case(ops, "bfloat16", m, n, k, epi, g, form="swapped", splits=splits) < KTOL["bfloat16"], (m, n, k, epi, splits)
+            try:
+                tcgen05_cluster_k(False)
+                assert linear_case(ops, "bfloat16", m, n, k, epi, g, form="swapped") < KTOL["bfloat16"], (m, n, k, epi)
+            finally:
+                tcgen05_cluster_k(True)
     assert linear_case(ops, "bfloat16", m, 333, 128, "store", g, bias=False, strided=True, form="swapped") < KTOL["bfloat16"]
     assert linear_case(ops, "bfloat16", m, 333, 128, "store_f32", g, bias_f32=True, form="swapped") < KTOL["bfloat16"]
     assert linear_case(ops, "bfloat16", m, 333, 128, "store", g, form="wide") < KTOL["bfloat16"]

@@ -432,6 +432,15 @@ class Ops:
                              _ptr(uniform), _ptr(out), _stream()), h)
 
 
+def sample_force_general(on: bool) -> None:
+    """Tests: True sends every sampling row through the selections over the whole vocabulary, also
+    where a small top-k has a shorter way."""
+    h = lib("sampling")
+    h.kvad_sample_force_general.argtypes = [c_int]
+    h.kvad_sample_force_general.restype = None
+    h.kvad_sample_force_general(int(bool(on)))
+
+
 def decode_force_plain(on) -> None:
     """Tests: 1 / True keeps the decode attention of every head size on the kernel that loads through
     registers; 2 keeps the TMA-fed kernel but merges splits through global memory, not a cluster; 0: default."""

@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 import torch
 
-from kvad_b200.ops import Ops
+from kvad_b200.ops import Ops, sample_force_general
 from kvad_b200.sampling import SamplingParams, sample_host, shortlist
 from tests.conftest import ROOT, random_tokens
 
@@ -76,6 +76,11 @@ def test_kernel_follows_the_rule(vocab):
     got = run_kernel(logits, params, us)
     again = run_kernel(logits, params, us)
     assert got == again                                  # the same logits, options and draw: the same token
+    sample_force_general(True)                           # and the same whichever way the kernel takes
+    try:
+        assert run_kernel(logits, params, us) == got
+    finally:
+        sample_force_general(False)
     exact = 0
     for i, tok in enumerate(got):
         want = sample_host(logits[i], params[i], us[i])
@@ -84,6 +89,35 @@ def test_kernel_follows_the_rule(vocab):
         else:
             assert on_a_boundary(logits[i], params[i], us[i], tok), (i, tok, want, params[i], us[i])
     assert exact >= 44
+
+
+@pytest.mark.parametrize("vocab", [300, 5000, 70001])
+def test_small_top_k_both_ways(vocab):
+    """Every top-k up to the short way's limit and beyond, on rows with and without ties, NaNs and -inf:
+    the short way and the selections over the whole vocabulary give the same tokens."""
+    rng = np.random.default_rng(7 * vocab)
+    rows, params, us = [], [], []
+    for i, k in enumerate([1, 2, 7, 40, 64, 65, 250, 511, 512, 900, 1024, 1025, 3000]):
+        l = rng.standard_normal(vocab).astype(np.float32) * (1 + i % 3)
+        if i % 3 == 1:
+            l = np.round(l * 2) / 2
+        if i % 4 == 2:
+            l[rng.integers(0, vocab, 20)] = np.nan
+            l[rng.integers(0, vocab, 20)] = -np.inf
+        rows.append(l)
+        params.append(SamplingParams([0.7, 1.0, 1.6][i % 3], k, [0.95, 1.0, 0.6][(i // 2) % 3]))
+        us.append(float(rng.random()))
+    logits = np.stack(rows)
+    got = run_kernel(logits, params, us)
+    sample_force_general(True)
+    try:
+        assert run_kernel(logits, params, us) == got
+    finally:
+        sample_force_general(False)
+    for i, tok in enumerate(got):
+        clean = np.where(np.isnan(logits[i]), -np.inf, logits[i])
+        want = sample_host(clean, params[i], us[i])
+        assert tok == want or on_a_boundary(clean, params[i], us[i], tok), (i, tok, want, params[i])
 
 
 def test_topk_one_and_greedy_agree_with_argmax():

@@ -13,11 +13,16 @@
 // The rows may continue a sequence that already has cached positions (a prompt in several steps):
 // a row's position is its sequence's length before the step plus its offset.  Query head h reads
 // key/value head h / (n_heads / n_kv_heads).  Head sizes: multiples of 16 up to 128; others are
-// refused and the caller uses the general kernel.
+// refused and the caller uses the general kernel.  Head sizes 64 and 128 run on the 5th-generation
+// tensor cores instead (attention_prefill_tc.cuh); this kernel serves the other head sizes.
 //
 // bisand/kvad: attend() per row, crates/llm/src/model/mod.rs:769-819; its candle path builds the
 // explicit mask instead (crates/gpu/src/gpt2.rs:249-276, crates/gpu/src/common.rs:1028-1042).
+#include <cstdio>
+#include <cstdlib>
+
 #include "common.cuh"
+#include "attention_prefill_tc.cuh"
 
 using namespace kvad;
 
@@ -264,14 +269,96 @@ int launch(const void* q, int64_t ld_q, void* out, int64_t ld_out, const int* se
   return KVAD_OK;
 }
 
+bool g_force_legacy = false;      // tests: keep every head size on the mma.sync kernel
+
+// A [rows, cols] bfloat16 matrix with row stride ld, loaded in boxes of box_rows x 64 with the 128-byte swizzle.
+int tile_map(const void* ptr, int64_t ld, int64_t rows, int cols, int box_rows, CUtensorMap* out) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) KVAD_FAIL(KVAD_ERR_CUDA, "attention_prefill: the driver does not offer cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    KVAD_FAIL(KVAD_ERR_CUDA, "attention_prefill: cuTensorMapEncodeTiled failed (%d) for a [%lld, %d] matrix with row stride %lld",
+              (int)r, (long long)rows, cols, (long long)ld);
+  return KVAD_OK;
+}
+
+template <int HD>
+int launch_tc(const void* q, int64_t ld_q, int n_rows, void* out, int64_t ld_out, const int* seq_starts, const int* kv_lens,
+              const int* page_table, int table_width, const void* k_pages, const void* v_pages, int64_t n_pages, int n_seqs,
+              int n_heads, int n_kv_heads, int max_new, float scale, int window, cudaStream_t stream) {
+  using L = pftc::Layout<HD>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(pftc::attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::SMEM);
+    if (e == cudaSuccess)       // all of the SM's shared memory, so that two CTAs of head size 64 fit
+      e = cudaFuncSetAttribute(pftc::attention_prefill_tc_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "attention_prefill: cannot reserve %zu bytes of shared memory: %s", (size_t)L::SMEM, cudaGetErrorString(e));
+    if (getenv("KVAD_DEBUG_OCCUPANCY")) {
+      int n = 0;
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, pftc::attention_prefill_tc_kernel<HD>, pftc::THREADS, L::SMEM);
+      cudaFuncAttributes fa;
+      cudaFuncGetAttributes(&fa, pftc::attention_prefill_tc_kernel<HD>);
+      size_t avail = 0;
+      for (size_t sm : {(size_t)0, (size_t)49152, (size_t)81920, (size_t)99464, (size_t)110000}) {
+        int k = 0;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&k, pftc::attention_prefill_tc_kernel<HD>, pftc::THREADS, sm);
+        fprintf(stderr, "  smem %zu -> %d CTAs\n", sm, k);
+      }
+      for (int th : {64, 128, 192, 256}) {
+        int k = 0;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&k, pftc::attention_prefill_tc_kernel<HD>, th, 0);
+        fprintf(stderr, "  threads %d -> %d CTAs\n", th, k);
+      }
+      cudaGetLastError();
+      fprintf(stderr, "attention_prefill_tc<%d>: %d CTAs per SM, %zu bytes of shared memory, %d registers, %zu static, %zu available for two\n",
+              HD, n, (size_t)L::SMEM, fa.numRegs, fa.sharedSizeBytes, avail);
+    }
+    configured = true;
+  }
+  CUtensorMap mq, mk, mv;
+  int rc = tile_map(q, ld_q, n_rows, n_heads * HD, pftc::ROWS, &mq);
+  if (rc != KVAD_OK) return rc;
+  rc = tile_map(k_pages, HD, n_pages * n_kv_heads * pftc::KEYS, HD, pftc::KEYS, &mk);
+  if (rc != KVAD_OK) return rc;
+  rc = tile_map(v_pages, HD, n_pages * n_kv_heads * pftc::KEYS, HD, pftc::KEYS, &mv);
+  if (rc != KVAD_OK) return rc;
+  const int n_q_tiles = (max_new + pftc::ROWS - 1) / pftc::ROWS;
+  const int n_pairs = (n_q_tiles + 1) / 2;        // a CTA takes a late tile and an early one
+  kvad_launch(pftc::attention_prefill_tc_kernel<HD>, dim3(n_pairs, n_heads, n_seqs), dim3(pftc::THREADS), L::SMEM, stream,
+              mq, mk, mv, (__nv_bfloat16*)out, ld_out, seq_starts, kv_lens, page_table, table_width, n_heads, n_kv_heads,
+              n_q_tiles, scale, window);
+  KVAD_CHECK_LAUNCH("attention_prefill_tc");
+  return KVAD_OK;
+}
+
 }  // namespace
+
+// Tests: 1 keeps head sizes 64 and 128 on the mma.sync kernel too.
+KVAD_EXPORT void kvad_attention_prefill_force_legacy(int on) { g_force_legacy = on != 0; }
+
+// How many bounded waits of the tcgen05 kernel have run out since the library was loaded (0 in a healthy run).
+KVAD_EXPORT int kvad_attention_prefill_status() {
+  int n = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&n, g_wait_timeouts, sizeof(int));
+  if (e != cudaSuccess) {
+    KVAD_FAIL(-1, "attention_prefill: cannot read the status word: %s", cudaGetErrorString(e));
+  }
+  return n;
+}
 
 // seq_starts[s]..seq_starts[s+1] are the packed rows of sequence s; kv_lens[s] its length after
 // this step; max_new the largest number of rows any sequence brings (sizes the grid).
-KVAD_EXPORT int kvad_attention_prefill(const void* q, int64_t ld_q, void* out, int64_t ld_out, const int* seq_starts,
+// n_rows: rows of q and out in all; n_pages: pages the cache tensors hold.
+KVAD_EXPORT int kvad_attention_prefill(const void* q, int64_t ld_q, int n_rows, void* out, int64_t ld_out, const int* seq_starts,
                                        const int* kv_lens, const int* page_table, int table_width, const void* k_pages,
-                                       const void* v_pages, int n_seqs, int n_heads, int n_kv_heads, int head_dim,
-                                       int page_size, int max_new, float scale, int window, cudaStream_t stream) {
+                                       const void* v_pages, int64_t n_pages, int n_seqs, int n_heads, int n_kv_heads,
+                                       int head_dim, int page_size, int max_new, float scale, int window, cudaStream_t stream) {
   KVAD_REQUIRE(n_seqs >= 0 && n_heads > 0 && n_kv_heads > 0 && table_width > 0 && max_new >= 0,
                "attention_prefill: bad sizes seqs=%d heads=%d kv_heads=%d", n_seqs, n_heads, n_kv_heads);
   KVAD_REQUIRE(n_heads % n_kv_heads == 0, "attention_prefill: %d heads do not divide into %d key/value heads", n_heads, n_kv_heads);
@@ -281,6 +368,13 @@ KVAD_EXPORT int kvad_attention_prefill(const void* q, int64_t ld_q, void* out, i
       (reinterpret_cast<uintptr_t>(k_pages) & 15) || (reinterpret_cast<uintptr_t>(v_pages) & 15))
     KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention_prefill: queries and cache must be 16-byte aligned with row strides that are multiples of 8");
   if (n_seqs == 0 || max_new == 0) return KVAD_OK;
+  if ((head_dim == 64 || head_dim == 128) && !g_force_legacy && ld_out % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    if (head_dim == 64)
+      return launch_tc<64>(q, ld_q, n_rows, out, ld_out, seq_starts, kv_lens, page_table, table_width, k_pages, v_pages, n_pages,
+                           n_seqs, n_heads, n_kv_heads, max_new, scale, window, stream);
+    return launch_tc<128>(q, ld_q, n_rows, out, ld_out, seq_starts, kv_lens, page_table, table_width, k_pages, v_pages, n_pages,
+                          n_seqs, n_heads, n_kv_heads, max_new, scale, window, stream);
+  }
 #define KVAD_PF_CASE(HD)                                                                                           \
   case HD:                                                                                                         \
     return launch<HD>(q, ld_q, out, ld_out, seq_starts, kv_lens, page_table, table_width, k_pages, v_pages, n_seqs, \

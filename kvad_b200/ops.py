@@ -65,8 +65,9 @@ _SIGNATURES = {
                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     },
     "attention_prefill": {
-        "kvad_attention_prefill": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                   c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "kvad_attention_prefill": [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
+                                   c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                   c_void_p],
     },
     "attention_decode": {
         "kvad_attention_decode_step": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
@@ -341,9 +342,10 @@ class Ops:
         if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
             raise KernelError("attention_prefill: tensors must be bfloat16")
         h = lib("attention_prefill")
-        _check(h.kvad_attention_prefill(_ptr(q), ld_q, _ptr(out), ld_o, _ptr(seq_starts), _ptr(kv_lens), _ptr(page_table),
-                                        page_table.shape[1], _ptr(k_pages), _ptr(v_pages), int(n_seqs), n_heads, n_kv, hd,
-                                        page, int(max_new), float(scale), int(window or 0), _stream()), h)
+        _check(h.kvad_attention_prefill(_ptr(q), ld_q, q.shape[0], _ptr(out), ld_o, _ptr(seq_starts), _ptr(kv_lens),
+                                        _ptr(page_table), page_table.shape[1], _ptr(k_pages), _ptr(v_pages),
+                                        k_pages.shape[0], int(n_seqs), n_heads, n_kv, hd, page, int(max_new), float(scale),
+                                        int(window or 0), _stream()), h)
 
     DECODE_HEAD_SIZES = (16, 32, 48, 64, 80, 96, 112, 128, 256)
 
@@ -439,6 +441,25 @@ def sample_force_general(on: bool) -> None:
     h.kvad_sample_force_general.argtypes = [c_int]
     h.kvad_sample_force_general.restype = None
     h.kvad_sample_force_general(int(bool(on)))
+
+
+def prefill_force_legacy(on: bool) -> None:
+    """Tests: True keeps the prompt attention of head sizes 64 and 128 on the mma.sync kernel, not the tcgen05 one."""
+    h = lib("attention_prefill")
+    h.kvad_attention_prefill_force_legacy.argtypes = [c_int]
+    h.kvad_attention_prefill_force_legacy.restype = None
+    h.kvad_attention_prefill_force_legacy(int(bool(on)))
+
+
+def prefill_wait_timeouts() -> int:
+    """How many bounded waits of the tcgen05 prompt attention have run out (0 in a healthy run)."""
+    h = lib("attention_prefill")
+    h.kvad_attention_prefill_status.argtypes = []
+    h.kvad_attention_prefill_status.restype = c_int
+    n = h.kvad_attention_prefill_status()
+    if n < 0:
+        raise KernelError(h.kvad_last_error().decode("utf-8", "replace"))
+    return n
 
 
 def decode_force_plain(on) -> None:

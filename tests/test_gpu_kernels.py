@@ -453,13 +453,27 @@ def test_attention_decode_finds_one_far_key():
 
 @pytest.mark.parametrize("hd,n_heads,n_kv,window", [(16, 4, 4, 0), (32, 3, 3, 0), (48, 6, 2, 0), (64, 12, 12, 0), (80, 3, 1, 0),
                                                     (96, 2, 2, 0), (112, 2, 1, 0), (128, 2, 2, 50), (64, 4, 2, 70), (32, 5, 5, 64)])
-def test_attention_prefill_tensor_cores(hd, n_heads, n_kv, window):
+@pytest.mark.parametrize("form", ["auto", "mma.sync"])
+def test_attention_prefill_tensor_cores(hd, n_heads, n_kv, window, form):
     """Whole prompts, prompts that continue cached positions, a single row and a row count that is no multiple
-    of the tile, in one launch; the pages hold NaN wherever no position lies."""
+    of the tile, in one launch; the pages hold NaN wherever no position lies.  Head sizes 64 and 128 run on
+    tcgen05 unless the older mma.sync kernel is forced."""
+    from kvad_b200.ops import prefill_force_legacy, prefill_wait_timeouts
+    if form == "mma.sync" and hd not in (64, 128):
+        pytest.skip("this head size has one kernel only")
+    prefill_force_legacy(form == "mma.sync")
+    try:
+        _attention_prefill_case(hd, n_heads, n_kv, window)
+    finally:
+        prefill_force_legacy(False)
+    assert prefill_wait_timeouts() == 0
+
+
+def _attention_prefill_case(hd, n_heads, n_kv, window):
     g = torch.Generator().manual_seed(3 * hd + n_heads + window)
     ops = Ops(torch.bfloat16)
-    lens = [200, 1, 64, 65, 300, 130]                 # lengths after the step
-    new = [200, 1, 64, 65, 37, 129]                   # rows the step brings (the rest was cached before)
+    lens = [200, 1, 64, 65, 300, 130, 650]            # lengths after the step
+    new = [200, 1, 64, 65, 37, 129, 600]              # rows the step brings (the rest was cached before)
     table, kp, vp, ks, vs = make_cache(g, "bfloat16", len(lens), lens, n_kv, hd)
     rows = [(s, p) for s, (l, n) in enumerate(zip(lens, new)) for p in range(l - n, l)]
     row_seq = torch.tensor([r[0] for r in rows], dtype=torch.int32)

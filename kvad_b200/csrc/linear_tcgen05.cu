@@ -62,7 +62,7 @@ template <int BN> struct Tile {
   static constexpr uint32_t B_BYTES = BN * BK * 2;
   static constexpr int STAGES_RAW = SMEM_BUDGET_WIDE / (A_BYTES + B_BYTES);
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  static constexpr int TMEM_COLS = BN < 32 ? 32 : (BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256)));   // a power of two
   // after the stages: the barriers, the bias of this tile as floats, and one 4 KB slab per epilogue warp
   // from which TMA stores (or reduce-adds) 32 rows x 128 bytes of output at a time
   static constexpr size_t SLAB_OFFSET = (((size_t)STAGES * (A_BYTES + B_BYTES) + (2 * STAGES + 1) * 8 + 16 + BN * 4) + 1023) / 1024 * 1024;
@@ -1145,7 +1145,7 @@ KVAD_EXPORT int kvad_linear_tcgen05_ln(const float* x, int64_t ldx, const int* r
 }
 
 // `force` fixes what the kernel otherwise chooses (tests): bits 0-15 the tile width of the wide
-// form (16, 32, 64, 128 or 256); bits 16-23 how many CTAs share K (residual epilogue only);
+// form (16, 32, 64, 128, 192 or 256); bits 16-23 how many CTAs share K (residual epilogue only);
 // bits 24-25 the form: 1 wide (activation rows on the M side), 2 swapped (at most 64 rows; the
 // tile width then means weight rows per CTA, 64 or 128).
 KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, const void* bias, int bias_f32,
@@ -1245,13 +1245,14 @@ KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, c
   const int kb_total = (K + BK - 1) / BK;
   int bn = force_bn, splits = 1;
   {
-    const int widths[5] = {256, 128, 64, 32, 16};
-    const float fixed_us[5] = {7.0f, 4.0f, 3.0f, 2.6f, 2.5f};
+    // (a kernel that allocates tensor memory has one CTA per SM, so a wave is 148 CTAs whatever their size)
+    const int widths[6] = {256, 192, 128, 64, 32, 16};
+    const float fixed_us[6] = {7.0f, 5.5f, 4.0f, 3.0f, 2.6f, 2.5f};
     float best = 1e30f;
-    for (int i = 0; i < 5; ++i) {
+    for (int i = 0; i < 6; ++i) {
       if (force_bn != 0 && widths[i] != force_bn) continue;
       const int64_t tiles = (int64_t)m_tiles * ((N + widths[i] - 1) / widths[i]);
-      for (int sp = 1; sp <= 8; sp *= 2) {
+      for (int sp = 1; sp <= 8; ++sp) {
         if (sp > 1 && (epilogue != EPI_RESIDUAL || kb_total / sp < 2)) break;
         if (force_splits > 0 && sp != 1) break;
         const int64_t waves = (tiles * sp + 147) / 148;
@@ -1260,7 +1261,8 @@ KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, c
       }
     }
   }
-  KVAD_REQUIRE(bn == 16 || bn == 32 || bn == 64 || bn == 128 || bn == 256, "linear_tcgen05: tile width %d is not one of 16, 32, 64, 128, 256", bn);
+  KVAD_REQUIRE(bn == 16 || bn == 32 || bn == 64 || bn == 128 || bn == 192 || bn == 256,
+               "linear_tcgen05: tile width %d is not one of 16, 32, 64, 128, 192, 256", bn);
   if (epilogue == EPI_RESIDUAL && force_splits > 0) splits = force_splits;
   if (splits > kb_total) splits = kb_total;
   if (splits < 1) splits = 1;
@@ -1276,6 +1278,7 @@ KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, c
     case 32: return launch_epi<32>(epilogue, ma, mw, bias, bias_f32, out, ldo, M, N, K, splits, stream);
     case 64: return launch_epi<64>(epilogue, ma, mw, bias, bias_f32, out, ldo, M, N, K, splits, stream);
     case 128: return launch_epi<128>(epilogue, ma, mw, bias, bias_f32, out, ldo, M, N, K, splits, stream);
+    case 192: return launch_epi<192>(epilogue, ma, mw, bias, bias_f32, out, ldo, M, N, K, splits, stream);
     default: return launch_epi<256>(epilogue, ma, mw, bias, bias_f32, out, ldo, M, N, K, splits, stream);
   }
 }

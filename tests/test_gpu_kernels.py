@@ -151,7 +151,7 @@ def test_linear_tensor_cores_shapes(m):
 
 
 @pytest.mark.parametrize("stores", ["tma", "plain"])
-@pytest.mark.parametrize("tile", [16, 32, 64, 128, 256])
+@pytest.mark.parametrize("tile", [16, 32, 64, 128, 192, 256])
 def test_linear_tensor_cores_every_tile_and_split(tile, stores):
     """Every tile width of the wide form, every split of K, output by TMA store / reduce-add and by plain stores."""
     ops = Ops(torch.bfloat16)

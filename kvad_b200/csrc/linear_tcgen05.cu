@@ -63,9 +63,10 @@ template <int BN> struct Tile {
   static constexpr int STAGES_RAW = SMEM_BUDGET_WIDE / (A_BYTES + B_BYTES);
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int TMEM_COLS = BN < 32 ? 32 : (BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256)));   // a power of two
-  // after the stages: the barriers, the bias of this tile as floats, and one 4 KB slab per epilogue warp
+  static constexpr int ACC_BUFS = 2;        // accumulators in tensor memory: the epilogue of one tile runs under the next one's products
+  // after the stages: the barriers, the bias of a tile as floats, and one 4 KB slab per epilogue warp
   // from which TMA stores (or reduce-adds) 32 rows x 128 bytes of output at a time
-  static constexpr size_t SLAB_OFFSET = (((size_t)STAGES * (A_BYTES + B_BYTES) + (2 * STAGES + 1) * 8 + 16 + BN * 4) + 1023) / 1024 * 1024;
+  static constexpr size_t SLAB_OFFSET = (((size_t)STAGES * (A_BYTES + B_BYTES) + (2 * STAGES + 2 * ACC_BUFS) * 8 + 16 + BN * 4) + 1023) / 1024 * 1024;
   static constexpr size_t SMEM = SLAB_OFFSET + 8 * 4096 + 1024;
 };
 
@@ -139,22 +140,27 @@ __device__ __forceinline__ void store_chunk(const float* v, void* out, int64_t l
   }
 }
 
+// One CTA per SM walks the tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (n fastest, then m, then the
+// K split): the ring of stages runs on from one tile into the next, and with two accumulators in tensor
+// memory the epilogue warps empty one while the MMAs fill the other.
 template <int BN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS_WIDE, 1)
 linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                       const __grid_constant__ CUtensorMap map_out, int tma_out,
                       const void* __restrict__ bias, int bias_f32, void* __restrict__ out, int64_t ldo,
-                      int M, int N, int K, int kb_per_split) {
+                      int M, int N, int K, int kb_per_split, int n_splits) {
   using T = Tile<BN>;
-  constexpr int STAGES = T::STAGES;
+  constexpr int STAGES = T::STAGES, ACC_BUFS = T::ACC_BUFS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* a_tiles = smem;
   uint8_t* b_tiles = smem + STAGES * T::A_BYTES;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(b_tiles + STAGES * T::B_BYTES);
   uint64_t* empty_bar = full_bar + STAGES;
-  uint64_t* tmem_full_bar = empty_bar + STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+  uint64_t* tmem_full_bar = empty_bar + STAGES;           // [ACC_BUFS] the accumulator is complete
+  uint64_t* tmem_empty_bar = tmem_full_bar + ACC_BUFS;    // [ACC_BUFS] the eight epilogue warps have read it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + ACC_BUFS);
+  float* bias_st = reinterpret_cast<float*>(tmem_slot + 4);   // [BN]
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -163,22 +169,34 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     prefetch_tensormap(&map_w);
     if (tma_out) prefetch_tensormap(&map_out);
   }
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int n_tiles_n = (N + BN - 1) / BN, n_tiles_m = (M + BM - 1) / BM;
+  const int n_tiles = n_tiles_n * n_tiles_m * n_splits;
   const int kb_total = (K + BK - 1) / BK;
-  const int kb_begin = blockIdx.z * kb_per_split;
-  const int kb_end = kb_begin + kb_per_split < kb_total ? kb_begin + kb_per_split : kb_total;
-  const int num_kb = kb_end - kb_begin;
+  // tile t: its corner and its share of K
+  auto tile_of = [&](int t, int* n0, int* m0, int* kb_begin, int* num_kb, int* z) {
+    const int nt = t % n_tiles_n, rest = t / n_tiles_n;
+    const int mt = rest % n_tiles_m;
+    *z = rest / n_tiles_m;
+    *n0 = nt * BN;
+    *m0 = mt * BM;
+    *kb_begin = *z * kb_per_split;
+    const int kb_end = *kb_begin + kb_per_split < kb_total ? *kb_begin + kb_per_split : kb_total;
+    *num_kb = kb_end - *kb_begin;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(tmem_full_bar, 1);
+    for (int b = 0; b < ACC_BUFS; ++b) {
+      mbar_init(&tmem_full_bar[b], 1);
+      mbar_init(&tmem_empty_bar[b], 8);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(tmem_slot, T::TMEM_COLS);
+  if (warp == 1) tmem_alloc(tmem_slot, ACC_BUFS * T::TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -186,60 +204,99 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 
   if (warp == 0) {
     if (lane == 0) {
-      // weights do not depend on the kernel before: their first stages are on the way before the wait
-      const int pre = num_kb < STAGES ? num_kb : STAGES;
-      for (int i = 0; i < pre; ++i) {
-        mbar_expect_tx(&full_bar[i], T::A_BYTES + T::B_BYTES);
-        tma_load_2d(b_tiles + i * T::B_BYTES, &map_w, &full_bar[i], (kb_begin + i) * BK, n0);
-      }
-      pdl_wait();
-      for (int i = 0; i < pre; ++i)
-        tma_load_2d(a_tiles + i * T::A_BYTES, &map_a, &full_bar[i], (kb_begin + i) * BK, m0);
-      for (int i = pre; i < num_kb; ++i) {
-        const int s = i % STAGES;
-        const uint32_t phase = (i / STAGES) & 1;
-        if (!mbar_wait(&empty_bar[s], phase ^ 1)) break;
-        mbar_expect_tx(&full_bar[s], T::A_BYTES + T::B_BYTES);
-        tma_load_2d(a_tiles + s * T::A_BYTES, &map_a, &full_bar[s], (kb_begin + i) * BK, m0);
-        tma_load_2d(b_tiles + s * T::B_BYTES, &map_w, &full_bar[s], (kb_begin + i) * BK, n0);
+      uint32_t it = 0;                       // stages filled so far, over all tiles
+      bool waited = false, ok = true;
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        int n0, m0, kb_begin, num_kb, z;
+        tile_of(t, &n0, &m0, &kb_begin, &num_kb, &z);
+        int i = 0;
+        if (!waited) {
+          // weights do not depend on the kernel before: the first tile's first stages are on the way before the wait
+          const int pre = num_kb < STAGES ? num_kb : STAGES;
+          for (int j = 0; j < pre; ++j) {
+            mbar_expect_tx(&full_bar[j], T::A_BYTES + T::B_BYTES);
+            tma_load_2d(b_tiles + j * T::B_BYTES, &map_w, &full_bar[j], (kb_begin + j) * BK, n0);
+          }
+          pdl_wait();
+          waited = true;
+          for (int j = 0; j < pre; ++j)
+            tma_load_2d(a_tiles + j * T::A_BYTES, &map_a, &full_bar[j], (kb_begin + j) * BK, m0);
+          i = pre;
+          it = pre;
+        }
+        for (; i < num_kb; ++i, ++it) {
+          const int s = it % STAGES;
+          if (it >= (uint32_t)STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1)) { ok = false; break; }
+          mbar_expect_tx(&full_bar[s], T::A_BYTES + T::B_BYTES);
+          tma_load_2d(a_tiles + s * T::A_BYTES, &map_a, &full_bar[s], (kb_begin + i) * BK, m0);
+          tma_load_2d(b_tiles + s * T::B_BYTES, &map_w, &full_bar[s], (kb_begin + i) * BK, n0);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc<BN>();
+      uint32_t it = 0;
+      int lt = 0;                            // tiles of this CTA so far
       bool ok = true;
-      for (int i = 0; i < num_kb && ok; ++i) {
-        const int s = i % STAGES;
-        const uint32_t phase = (i / STAGES) & 1;
-        ok = mbar_wait(&full_bar[s], phase);
-        if (!ok) break;
-        tc_fence_after();
-        const uint64_t a_desc = sw128_desc(smem_u32(a_tiles + s * T::A_BYTES));
-        const uint64_t b_desc = sw128_desc(smem_u32(b_tiles + s * T::B_BYTES));
-#pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          // 16 elements further along K: 32 bytes inside the swizzled row, i.e. 2 in units of 16 bytes
-          umma(tmem_base, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
+        int n0, m0, kb_begin, num_kb, z;
+        tile_of(t, &n0, &m0, &kb_begin, &num_kb, &z);
+        const int buf = lt % ACC_BUFS;
+        if (lt >= ACC_BUFS) {                // the epilogue has emptied this accumulator
+          ok = mbar_wait(&tmem_empty_bar[buf], ((lt / ACC_BUFS) & 1) ^ 1);
+          if (!ok) break;
+          tc_fence_after();
         }
-        umma_commit(&empty_bar[s]);     // the stage is free again once these MMAs have read it
+        const uint32_t acc = tmem_base + (uint32_t)(buf * T::TMEM_COLS);
+        for (int i = 0; i < num_kb; ++i, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(&full_bar[s], (it / STAGES) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t a_desc = sw128_desc(smem_u32(a_tiles + s * T::A_BYTES));
+          const uint64_t b_desc = sw128_desc(smem_u32(b_tiles + s * T::B_BYTES));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // 16 elements further along K: 32 bytes inside the swizzled row, i.e. 2 in units of 16 bytes
+            umma(acc, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);     // the stage is free again once these MMAs have read it
+        }
+        if (!ok) break;
+        umma_commit(&tmem_full_bar[buf]); // the accumulator is complete once everything issued has run
       }
-      umma_commit(tmem_full_bar);       // the accumulator is complete once everything issued has run
     }
   } else {
     const int quarter = warp & 3;       // the 32 tensor-memory lanes this warp may read
-    const int row = m0 + quarter * 32 + lane;
-    if (tma_out) {                        // this tile's bias, as floats, while the product runs
-      float* bias_st = reinterpret_cast<float*>(tmem_slot + 4);
-      for (int j = threadIdx.x - 64; j < BN; j += NUM_THREADS_WIDE - 64)
-        bias_st[j] = (bias != nullptr && n0 + j < N) ? load_param(bias, n0 + j, bias_f32) : 0.f;
-      asm volatile("bar.sync 1, 256;" ::: "memory");     // the eight epilogue warps
-    }
-    pdl_wait();
-    const bool ok = mbar_wait(tmem_full_bar, 0);
-    tc_fence_after();
-    if (ok) {
-      const bool add_bias = blockIdx.z == 0;
-      const bool atomic = gridDim.z > 1;
+    bool waited = false, slab_used = false, dead = false;
+    int lt = 0;
+    for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++lt) {
+      int n0, m0, kb_begin, num_kb, z;
+      tile_of(t, &n0, &m0, &kb_begin, &num_kb, &z);
+      const int buf = lt % ACC_BUFS;
+      const uint32_t acc = tmem_base + (uint32_t)(buf * T::TMEM_COLS) + ((uint32_t)(quarter * 32) << 16);
+      const int row = m0 + quarter * 32 + lane;
+      float* bias_sh = bias_st;
+      if (tma_out) {                        // this tile's bias, as floats, while the product runs
+        if (lt > 0) asm volatile("bar.sync 1, 256;" ::: "memory");   // all eight warps are done with the last tile's
+        for (int j = threadIdx.x - 64; j < BN; j += NUM_THREADS_WIDE - 64)
+          bias_sh[j] = (bias != nullptr && n0 + j < N) ? load_param(bias, n0 + j, bias_f32) : 0.f;
+        asm volatile("bar.sync 1, 256;" ::: "memory");     // the eight epilogue warps
+      }
+      if (!waited) {
+        pdl_wait();
+        waited = true;
+      }
+      // (a warp whose wait ran out goes on through the loop without working, so that it still meets the
+      // others at the barrier above)
+      if (dead || !mbar_wait(&tmem_full_bar[buf], (lt / ACC_BUFS) & 1)) {
+        dead = true;
+        continue;
+      }
+      tc_fence_after();
+      const bool add_bias = z == 0;
+      const bool atomic = n_splits > 1;
       // two warps share a quarter of the lanes: the first takes the left half of the columns, the second the right
       constexpr int HALF = BN >= 32 ? BN / 2 : BN;
       const int c_begin = (BN >= 32 && warp >= 6) ? HALF : 0;
@@ -249,25 +306,25 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         constexpr bool F32_OUT = (EPI == EPI_RESIDUAL || EPI == EPI_STORE_F32);
         constexpr int SLAB_COLS = F32_OUT ? 32 : 64;              // 128 bytes of output per row
         uint8_t* slab = smem + T::SLAB_OFFSET + (size_t)(warp - 2) * 4096;
-        const float* bias_sh = reinterpret_cast<const float*>(tmem_slot + 4);
         // the two warps of a quarter take alternate slabs
         const int first = (warp >= 6 ? 1 : 0) * SLAB_COLS;
 #pragma unroll 1
         for (int c0 = first; c0 < BN; c0 += 2 * SLAB_COLS) {
-          if (c0 > first) {                                         // the slab's last journey has been read
+          if (slab_used) {                                          // the slab's last journey has been read
             if (lane == 0) bulk_wait_read();
             __syncwarp();
           }
+          slab_used = true;
 #pragma unroll
           for (int cc = 0; cc < SLAB_COLS; cc += 16) {
             float v[16];
-            tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c0 + cc), v);
+            tmem_ld16(acc + (uint32_t)(c0 + cc), v);
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              float t = v[j] + (add_bias ? bias_sh[c0 + cc + j] : 0.f);
-              if (EPI == EPI_GELU_TANH) t = gelu_tanh_fast(t);
-              if (EPI == EPI_GELU_ERF) t = gelu_erf(t);
-              v[j] = t;
+              float x = v[j] + (add_bias ? bias_sh[c0 + cc + j] : 0.f);
+              if (EPI == EPI_GELU_TANH) x = gelu_tanh_fast(x);
+              if (EPI == EPI_GELU_ERF) x = gelu_erf(x);
+              v[j] = x;
             }
             if (F32_OUT) {
 #pragma unroll
@@ -296,17 +353,21 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             bulk_commit();
           }
         }
-        if (lane == 0) bulk_wait_all();
       } else {
 #pragma unroll 1
         for (int c = c_begin; c < c_end; c += 16) {
           float v[16];
-          tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, v);   // all lanes take part
+          tmem_ld16(acc + (uint32_t)c, v);   // all lanes take part
           if (row < M && n0 + c < N)
             store_chunk<EPI, 16>(v, out, ldo, row, n0 + c, N, bias, bias_f32, add_bias, atomic);
         }
       }
+      // this warp has read its share of the accumulator: the MMAs of the tile after next may overwrite it
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_one(&tmem_empty_bar[buf]);
     }
+    if (lane == 0) bulk_wait_all();
   }
 
   tc_fence_before();
@@ -314,7 +375,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   tc_fence_after();
   if (warp == 1) {
     __syncwarp();
-    tmem_dealloc(tmem_base, T::TMEM_COLS);
+    tmem_dealloc(tmem_base, ACC_BUFS * T::TMEM_COLS);
   }
 }
 
@@ -970,6 +1031,16 @@ int tensor_map_3d(const void* ptr, int64_t ld, int rows, int cols, int box_rows,
   return KVAD_OK;
 }
 
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) n = v;
+    else n = 148;
+  }
+  return n;
+}
+
 template <int BN, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, const void* bias, int bias_f32, void* out, int64_t ldo,
            int M, int N, int K, int splits, cudaStream_t stream) {
@@ -993,8 +1064,11 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, const void* bias, int b
   const int kb_total = (K + BK - 1) / BK;
   const int kb_per_split = (kb_total + splits - 1) / splits;
   const int z = (kb_total + kb_per_split - 1) / kb_per_split;
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, z);
-  kvad_launch(linear_tcgen05_kernel<BN, EPI>, grid, dim3(NUM_THREADS_WIDE), T::SMEM, stream, ma, mw, mo, tma_out, bias, bias_f32, out, ldo, M, N, K, kb_per_split);
+  const int64_t n_tiles = (int64_t)((N + BN - 1) / BN) * ((M + BM - 1) / BM) * z;
+  KVAD_REQUIRE(n_tiles < (1ll << 30), "linear_tcgen05: %lld tiles are more than one launch takes", (long long)n_tiles);
+  const int ctas = n_tiles < sm_count() ? (int)n_tiles : sm_count();      // one CTA per SM walks the tiles
+  kvad_launch(linear_tcgen05_kernel<BN, EPI>, dim3(ctas), dim3(NUM_THREADS_WIDE), T::SMEM, stream, ma, mw, mo, tma_out, bias,
+              bias_f32, out, ldo, M, N, K, kb_per_split, z);
   KVAD_CHECK_LAUNCH("linear_tcgen05");
   return KVAD_OK;
 }

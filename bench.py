@@ -104,17 +104,20 @@ def random_prompts(n, length, vocab, seed):
     return [rng.integers(0, vocab, length).tolist() for _ in range(n)]
 
 
-def decode_point(engine, batch, prompt_len, steps, warmup, seed, clock=False):
-    """Device-timed decoding: prompts in one step, `warmup` untimed steps, then exactly `steps` steps."""
+def decode_point(engine, batch, prompt_len, steps, warmup, seed, clock=False, sampled=False):
+    """Device-timed decoding: prompts in one step, `warmup` untimed steps, then exactly `steps` steps.
+    `sampled`: every request draws with temperature 0.7, top-k 40, top-p 0.95 instead of taking the best token."""
     import torch
     from kvad_b200 import StepEntry
+    from kvad_b200.sampling import RequestSampler, SamplingParams
 
     prompts = random_prompts(batch, prompt_len, engine.vocab_size, seed)
     slots = [engine.open() for _ in prompts]
+    samplers = [RequestSampler(SamplingParams(0.7, 40, 0.95, seed + i)) for i in range(batch)] if sampled else None
     try:
         logits = engine.step([StepEntry(s, p, (len(p) - 1,)) for s, p in zip(slots, prompts)])
         first = logits.argmax(dim=-1).tolist()
-        hist = engine.decode_run(slots, first, warmup)
+        hist = engine.decode_run(slots, first, warmup, samplers)
         nxt = hist[-1].tolist()
         torch.cuda.synchronize()
         k0, start, end = engine.graph_kernels, torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -123,7 +126,7 @@ def decode_point(engine, batch, prompt_len, steps, warmup, seed, clock=False):
             sampler.__enter__()
         torch.cuda.synchronize()
         start.record()
-        engine.decode_run(slots, nxt, steps)
+        engine.decode_run(slots, nxt, steps, samplers)
         end.record()
         torch.cuda.synchronize()
         if sampler:
@@ -193,6 +196,8 @@ def main():
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profiling)")
     ap.add_argument("--phase", default="all", choices=["all", "prefill"], help="`prefill`: only the 2 x 1024-token prefill (profiling)")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64, prefill and e2e (quick runs)")
+    ap.add_argument("--sampling", default="greedy", choices=["greedy", "sampled"],
+                    help="`sampled`: the timed decode steps draw with temperature 0.7, top-k 40, top-p 0.95")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -229,7 +234,7 @@ def main():
                           "tflops": round(fl / (t_ms * 1e-3) / 1e12, 2), "frac": round(fl / (t_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
                           "of": pk_src}))
         return 0
-    main_pt = decode_point(engine, args.batch, args.prompt_len, args.steps, warmup, seed=1, clock=True)
+    main_pt = decode_point(engine, args.batch, args.prompt_len, args.steps, warmup, seed=1, clock=True, sampled=args.sampling == "sampled")
     bytes_step = decode_bytes(engine, args.batch, main_pt["mean_ctx"])
     achieved = bytes_step / (main_pt["ms_per_step"] * 1e-3) / 1e9
     out = {
@@ -242,7 +247,7 @@ def main():
                    "parallelism": "single-gpu", "prompt_len": args.prompt_len, "decode_steps": args.steps,
                    "n_layer": n_layers_full, "n_layer_run": args.layers, "n_embd": cfg["n_embd"], "n_head": cfg["n_head"],
                    "n_inner": cfg["n_inner"], "vocab_size": cfg["vocab_size"], "n_positions": cfg["n_positions"],
-                   "sampling": "greedy", "weights": "random seed 0", "cache_page_tokens": 64,
+                   "sampling": "greedy" if args.sampling == "greedy" else "temperature 0.7, top-k 40, top-p 0.95", "weights": "random seed 0", "cache_page_tokens": 64,
                    "l2": "inputs larger than L2: a step streams %.0f MB" % (bytes_step / 1e6),
                    "peaks": pk_src},
         "gpu_launches": int(main_pt["launches"]),
@@ -276,6 +281,8 @@ def main():
             points[f"decode_b{b}"] = round(pt["tok_s"], 1)
             by = decode_bytes(engine, b, pt["mean_ctx"])
             points[f"decode_b{b}_hbm_frac"] = round(by / (pt["ms_per_step"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        pt = decode_point(engine, args.batch, args.prompt_len, min(args.steps, 128), warmup, seed=30, sampled=True)
+        points[f"decode_b{args.batch}_sampled"] = round(pt["tok_s"], 1)      # temperature 0.7, top-k 40, top-p 0.95
         out["points"] = points
 
     from kvad_b200.csrc import build

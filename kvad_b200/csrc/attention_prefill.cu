@@ -368,7 +368,7 @@ KVAD_EXPORT int kvad_attention_prefill(const void* q, int64_t ld_q, int n_rows, 
       (reinterpret_cast<uintptr_t>(k_pages) & 15) || (reinterpret_cast<uintptr_t>(v_pages) & 15))
     KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention_prefill: queries and cache must be 16-byte aligned with row strides that are multiples of 8");
   if (n_seqs == 0 || max_new == 0) return KVAD_OK;
-  if ((head_dim == 64 || head_dim == 128) && !g_force_legacy && ld_out % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+  if ((head_dim == 64 || head_dim == 128) && !g_force_legacy && scale > 0.f && ld_out % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
     if (head_dim == 64)
       return launch_tc<64>(q, ld_q, n_rows, out, ld_out, seq_starts, kv_lens, page_table, table_width, k_pages, v_pages, n_pages,
                            n_seqs, n_heads, n_kv_heads, max_new, scale, window, stream);

@@ -303,26 +303,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       tmem_ld_wait();
       const bool mask = (j * KEYS + KEYS - 1 > me.pos0) || (window > 0 && j * KEYS <= pos_last_row - window);
       // (two loops, so that the pages every row sees whole carry no per-element test; four running maxima
-      // keep the chain of dependent instructions short)
+      // keep the chain of dependent instructions short.  The scale, which is positive, is applied to the
+      // maximum here and to each score inside the exponent's multiply-add below.)
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (!mask) {
 #pragma unroll
-        for (int c = 0; c < KEYS; ++c) {
-          const float v = __uint_as_float(sr[c]) * sl2;
-          sr[c] = __float_as_uint(v);
-          mx[c & 3] = fmaxf(mx[c & 3], v);
-        }
+        for (int c = 0; c < KEYS; ++c) mx[c & 3] = fmaxf(mx[c & 3], __uint_as_float(sr[c]));
       } else {
         const int lo_key = window > 0 ? pos - window + 1 : 0;       // the row sees keys lo_key .. pos
 #pragma unroll
         for (int c = 0; c < KEYS; ++c) {
           const int key = j * KEYS + c;
-          const float v = (key <= pos && key >= lo_key) ? __uint_as_float(sr[c]) * sl2 : -INFINITY;
+          const float v = (key <= pos && key >= lo_key) ? __uint_as_float(sr[c]) : -INFINITY;
           sr[c] = __float_as_uint(v);
           mx[c & 3] = fmaxf(mx[c & 3], v);
         }
       }
-      const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * sl2;
       const float new_max = fmaxf(run_max, tile_max);
       const float base = new_max == -INFINITY ? 0.f : new_max;        // a row that has seen nothing yet
       const float keep = run_max == -INFINITY ? 0.f : fast_exp2(run_max - base);
@@ -334,8 +331,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         uint32_t w[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float p0 = fast_exp2(__uint_as_float(sr[ch * 8 + 2 * e]) - base);
-          const float p1 = fast_exp2(__uint_as_float(sr[ch * 8 + 2 * e + 1]) - base);
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[ch * 8 + 2 * e]), sl2, -base));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[ch * 8 + 2 * e + 1]), sl2, -base));
           sum2[0] += p0;
           sum2[1] += p1;
           __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);

@@ -276,3 +276,23 @@ def test_repeated_step_shapes_replay_a_graph_with_the_same_result(engines, plain
         assert rel_err(got, ref) < TOL["bfloat16"], rep
         e.close(sa), e.close(sb)
     assert len([v for v in e._graphs.values() if v != "seen"]) > before
+
+
+def test_random_weights_entry_point(tmp_path):
+    """Engine.random writes a model folder from a configuration and a seed and loads it like any other: the folder
+    it leaves gives the plain implementation the same weights, and the same seed gives the same model without one."""
+    from kvad_b200 import Engine
+    from tests.plain.gpt2_plain import PlainGpt2
+    d = str(tmp_path / "m")
+    e = Engine.random(TINY["B"], seed=5, dtype="float32", model_dir=d, max_tokens=1024)
+    plain = PlainGpt2(d)
+    prompt = random_tokens(3, 11, TINY["B"]["vocab_size"])
+    got = e.generate([prompt], max_tokens=6, temperature=0.0, stop_token_ids=[])[0]
+    seq = list(prompt)
+    for _ in range(6):
+        seq.append(int(np.argmax(plain.logits(seq)[-1])))
+    assert got == seq[len(prompt):]
+    again = Engine.random(TINY["B"], seed=5, dtype="float32", max_tokens=1024)
+    assert again.generate([prompt], max_tokens=6, temperature=0.0, stop_token_ids=[])[0] == got
+    other = Engine.random(TINY["B"], seed=6, dtype="float32", max_tokens=1024)
+    assert other.generate([prompt], max_tokens=6, temperature=0.0, stop_token_ids=[])[0] != got

@@ -182,3 +182,31 @@ def test_head_alone_tied_and_untied(step, dtype):
         assert rel(logits, ref) < PTOL[dtype], tied
         if tied:
             assert head.proj.weight.data_ptr() == emb.weight.data_ptr()           # no second copy of the table
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_block_alone(step, dtype, plains):
+    """The pre-norm arrangement built from the plan's own spec with weights of its own names, on rows that are
+    no model's activations: x += mixer(norm1(x)); x += feed_forward(norm2(x)), on cache entry 1."""
+    e, ctx, _, toks = step(dtype)
+    plain = plains("A")
+    spec = e.model.plan.blocks[1]
+    block = build_part("block", spec, "blk.")
+    assert [type(c).__name__ for c in block.children()] == ["LayerNorm", "CausalSelfAttention", "LayerNorm", "DenseMLP"]
+    # the part's requests name what it wants; feed it layer 1's tensors of tiny A under those names
+    theirs = {r.name: r for r in e.model.blocks[1].requests()}
+    mine = {r.name: r for r in block.requests()}
+    assert len(theirs) == len(mine) == 12
+    rename = {m: t for m, t in zip(sorted(mine), sorted(theirs))}     # same suffixes, other prefix: same order
+    assert all(m.split(".", 1)[1] == t.split(".", 2)[2] for m, t in rename.items()), rename
+    tensors = {m: torch.from_numpy(np.asarray(plain.w[t])) for m, t in rename.items()}
+    block.load(fetch_from(tensors, DT[dtype]))
+    g = torch.Generator().manual_seed(11)
+    x0 = torch.randn(ctx.n_rows, 64, generator=g)
+    x = x0.clone().cuda()
+    block.forward(ctx, x, LayerCall(1, 1))
+    ref, off = [], 0
+    for tk in toks:
+        ref.append(plain.block(x0[off:off + len(tk)].double().numpy(), 1))
+        off += len(tk)
+    assert rel(x, np.concatenate(ref)) < PTOL[dtype] * (3 if dtype == "bfloat16" else 1)

@@ -15,10 +15,13 @@ SHAPES = {
                layer_norm_epsilon=1e-5, activation_function="gelu_new"),
     "medium": dict(model_type="gpt2", n_layer=2, n_embd=1024, n_head=16, n_inner=4096, vocab_size=2000, n_positions=512,
                    layer_norm_epsilon=1e-5, activation_function="gelu_new"),
+    # four heads of 128 over two key/value heads: the tcgen05 prompt attention at its other head size, grouped
+    "heads128": dict(model_type="gpt2", n_layer=2, n_embd=512, n_head=4, num_key_value_heads=2, head_dim=128, n_inner=1024,
+                     vocab_size=1500, n_positions=512, layer_norm_epsilon=1e-5, activation_function="gelu_new"),
 }
 
 
-@pytest.mark.parametrize("name", ["xl", "medium"])
+@pytest.mark.parametrize("name", ["xl", "medium", "heads128"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_large_layer_sizes(tmp_path, name, dtype):
     cfg = SHAPES[name]

@@ -510,20 +510,32 @@ attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict
     }
     cluster_sync_all();
     if (split == 0) {
-      float gm = -INFINITY;
-      for (int s2 = 0; s2 < n_splits; ++s2) gm = fmaxf(gm, ld_cluster_f32(&part_sh[HD], (unsigned)s2));
-      float gl = 0.f;
-      for (int s2 = 0; s2 < n_splits; ++s2) {
-        const float ms = ld_cluster_f32(&part_sh[HD], (unsigned)s2);
-        if (ms != -INFINITY) gl += ld_cluster_f32(&part_sh[HD + 1], (unsigned)s2) * exp_for<T>(ms - gm);
+      // (every load is issued before the first is used: one trip through the cluster's network per phase)
+      float ms[8], ws[8];
+#pragma unroll
+      for (int s2 = 0; s2 < 8; ++s2) {
+        ms[s2] = s2 < n_splits ? ld_cluster_f32(&part_sh[HD], (unsigned)s2) : -INFINITY;
+        ws[s2] = s2 < n_splits ? ld_cluster_f32(&part_sh[HD + 1], (unsigned)s2) : 0.f;
       }
+      float gm = -INFINITY;
+#pragma unroll
+      for (int s2 = 0; s2 < 8; ++s2) gm = fmaxf(gm, ms[s2]);
+      float gl = 0.f;
+#pragma unroll
+      for (int s2 = 0; s2 < 8; ++s2) {
+        const float a = ms[s2] == -INFINITY ? 0.f : exp_for<T>(ms[s2] - gm);
+        gl += ws[s2] * a;                 // (the sum in rank order, as before)
+        ws[s2] = a;
+      }
+      const float inv = 1.0f / gl;
       for (int d = tid; d < HD; d += TMA_THREADS) {
+        float v[8];
+#pragma unroll
+        for (int s2 = 0; s2 < 8; ++s2) v[s2] = s2 < n_splits ? ld_cluster_f32(&part_sh[d], (unsigned)s2) : 0.f;
         float o = 0.f;
-        for (int s2 = 0; s2 < n_splits; ++s2) {
-          const float ms = ld_cluster_f32(&part_sh[HD], (unsigned)s2);
-          if (ms != -INFINITY) o += ld_cluster_f32(&part_sh[d], (unsigned)s2) * exp_for<T>(ms - gm);
-        }
-        out[(int64_t)r * ld_out + (int64_t)h * HD + d] = from_f32<T>(o / gl);
+#pragma unroll
+        for (int s2 = 0; s2 < 8; ++s2) o += v[s2] * ws[s2];
+        out[(int64_t)r * ld_out + (int64_t)h * HD + d] = from_f32<T>(o * inv);
       }
     }
     cluster_sync_all();          // nobody's shared memory goes away while the first CTA reads it

@@ -1236,7 +1236,18 @@ KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, c
 
   const int force_bn = force & 0xffff, force_splits = (force >> 16) & 0xff, force_path = (force >> 24) & 3;
   KVAD_REQUIRE(force_path != 2 || M <= 64, "linear_tcgen05: the swapped form takes at most 64 rows, not %d", M);
-  if ((M <= 64 && force_path != 1 && force_bn == 0) || force_path == 2) {
+  // Up to 16 rows the swapped form always; up to 64 rows too, except where its epilogue, which grows with the
+  // rows (every thread stores a column of the transposed output, two bytes at a time), costs more than the wide
+  // form's fixed tile: measured on a B200 at K = 768 and 3072, the wide form with 64-wide tiles takes the same
+  // time from 17 to 64 rows (out-projection 2.9 us, up-projection 6.2 us, down-projection 4.4 us), the swapped
+  // form 3.1 -> 4.7, 5.7 -> 7.5 and 4.0 -> 5.6 us from 24 to 64 rows.  The choice depends on the row count's
+  // class and the epilogue only.
+  bool swapped = (M <= 64 && force_path != 1 && force_bn == 0) || force_path == 2;
+  if (swapped && force_path == 0 && M > 16) {
+    const bool gelu = epilogue == EPI_GELU_TANH || epilogue == EPI_GELU_ERF;
+    if ((epilogue == EPI_RESIDUAL && M >= 24) || (gelu && M >= 48)) swapped = false;
+  }
+  if (swapped) {
     // few rows: weights on the M side of the MMA, 64 rows a CTA unless that makes more CTAs than SMs
     const int mb = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     const int kb_all = (K + BK - 1) / BK;
@@ -1321,7 +1332,7 @@ KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, c
   {
     // (a kernel that allocates tensor memory has one CTA per SM, so a wave is 148 CTAs whatever their size)
     const int widths[6] = {256, 192, 128, 64, 32, 16};
-    const float fixed_us[6] = {7.0f, 5.5f, 4.0f, 3.0f, 2.6f, 2.5f};
+    const float fixed_us[6] = {7.0f, 5.5f, 4.0f, 3.0f, 3.4f, 3.6f};      // (narrower than 64 buys nothing: measured)
     float best = 1e30f;
     for (int i = 0; i < 6; ++i) {
       if (force_bn != 0 && widths[i] != force_bn) continue;

@@ -414,6 +414,17 @@ attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict
     float qreg[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) qreg[i] = to_f32(q[(int64_t)r * ld_q + (int64_t)h * HD + c * 8 + i]);
+    // the step's own key and value, where they are handed in, replace what the page holds at the row's
+    // position; they are fetched once, and chosen by a select where the loops below meet that position
+    float k_own[8], v_own[8];
+    const bool own = k_row_new != nullptr && pos >= t_begin && pos < t_end;
+    if (own) {
+      Vec8<T>::load(k_row_new + c * 8, k_own);
+      Vec8<T>::load(v_row_new + c * 8, v_own);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) k_own[e] = v_own[e] = 0.f;
+    }
     for (int i = 0; i < n_tiles; ++i) {
       const int s = i % STAGES;
       if (!dec_mbar_wait(&full_bar[s], (i / STAGES) & 1)) break;
@@ -428,8 +439,10 @@ attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict
         const int t = tile_key0 + key;
         const bool valid = (pass * KPP + kl < WARP_KEYS) && t >= t_begin && t < t_end;
         float f[8];
-        if (k_row_new != nullptr && t == pos) Vec8<T>::load(k_row_new + c * 8, f);
-        else Vec8<T>::load(Kt + key * HD + c * 8, f);
+        Vec8<T>::load(Kt + key * HD + c * 8, f);
+        const bool mine = own && t == pos;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = mine ? k_own[e] : f[e];
         float dot = 0.f;
 #pragma unroll
         for (int e = 0; e < 8; ++e) dot = fmaf(qreg[e], f[e], dot);
@@ -449,14 +462,20 @@ attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict
       for (int pass = 0; pass < PASSES; ++pass) {
         const int key = warp * WARP_KEYS + pass * KPP + kl;
         const int t = tile_key0 + key;
-        if (sc[pass] != -INFINITY) {                  // a key outside the range adds nothing, whatever its page holds
-          const float p = exp_for<T>(sc[pass] - new_max);
+        {
+          // a key outside the range adds nothing, whatever its page holds: its weight is 0 and its value is
+          // replaced by 0 (a stale page may hold NaN)
+          const bool in_range = sc[pass] != -INFINITY;
+          const float p = in_range ? exp_for<T>(sc[pass] - new_max) : 0.f;
           chunk_sum += p;
           float f[8];
-          if (v_row_new != nullptr && t == pos) Vec8<T>::load(v_row_new + c * 8, f);
-          else Vec8<T>::load(Vt + key * HD + c * 8, f);
+          Vec8<T>::load(Vt + key * HD + c * 8, f);
+          const bool mine = own && t == pos;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) acc[e] = fmaf(p, f[e], acc[e]);
+          for (int e = 0; e < 8; ++e) {
+            const float val = mine ? v_own[e] : (in_range ? f[e] : 0.f);
+            acc[e] = fmaf(p, val, acc[e]);
+          }
         }
       }
 #pragma unroll

@@ -98,6 +98,40 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The two halves of that meeting, for a CTA that has something else to do in between (every thread of the
+// cluster arrives once; those that need the others' arrival wait).
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// A float into the shared memory of CTA `rank` of this cluster, at the place `local` has in this CTA's.
+__device__ __forceinline__ void st_cluster_f32(float* local, unsigned rank, float v) {
+  unsigned addr = (unsigned)__cvta_generic_to_shared(local), remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+// Four floats (16-byte aligned) into the shared memory of CTA `rank`, at the place `local` has in this CTA's.
+__device__ __forceinline__ void st_cluster_f32x4(float* local, unsigned rank, float4 v) {
+  unsigned addr = (unsigned)__cvta_generic_to_shared(local), remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+// Arrives on the mbarrier that CTA `rank` of this cluster has at the place `local_bar` has here; what this
+// thread (and, after a __syncwarp, its warp) wrote to that CTA's shared memory before is visible to whoever
+// sees the arrival.
+__device__ __forceinline__ void mbar_arrive_cluster(uint64_t* local_bar, unsigned rank) {
+  unsigned addr = (unsigned)__cvta_generic_to_shared(local_bar), remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
+// One poll of an mbarrier of this CTA on which other CTAs of the cluster arrive.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"((unsigned)__cvta_generic_to_shared(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
 // A float from the shared memory of CTA `rank` of this cluster, at the place `local` has in this CTA's.
 __device__ __forceinline__ float ld_cluster_f32(const float* local, unsigned rank) {
   unsigned addr = (unsigned)__cvta_generic_to_shared(local), remote;

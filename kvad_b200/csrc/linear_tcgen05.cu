@@ -551,7 +551,9 @@ linear_tcgen05_skinny3d_kernel(const __grid_constant__ CUtensorMap map_a, const 
   uint64_t* a_full = w_empty + stages;
   uint64_t* tmem_full_bar = a_full + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
-  float* red_sh = reinterpret_cast<float*>(tmem_slot + 4);             // [MB][128]: this CTA's partial sums (cluster_reduce)
+  uint64_t* recv_bar = reinterpret_cast<uint64_t*>(tmem_slot + 4);     // credited with the partial sums the cluster's CTAs send here
+  float* recv_sh = reinterpret_cast<float*>(recv_bar + 2);             // [ranks][rows of this CTA][128] received (cluster_reduce)
+  float* part_sh = recv_sh + (size_t)(MB + 8) * BM;                    // [MB][128] this CTA's own partial sums, to be sent
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -573,6 +575,7 @@ linear_tcgen05_skinny3d_kernel(const __grid_constant__ CUtensorMap map_a, const 
     }
     mbar_init(a_full, 1);
     mbar_init(tmem_full_bar, 1);
+    mbar_init(recv_bar, 4 * gridDim.y);                    // the four epilogue warps of every CTA of the cluster
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -592,6 +595,13 @@ linear_tcgen05_skinny3d_kernel(const __grid_constant__ CUtensorMap map_a, const 
       pdl_wait();
       mbar_expect_tx(a_full, (uint32_t)kb_per_split * A_BYTES);
       tma_load_3d(a_all, &map_a, a_full, 0, 0, kb_begin);
+    }
+    // (every thread of the cluster arrives at its barrier once, early; the epilogue warps wait on it much later,
+    // just before they write into the other CTAs' shared memory, whose barriers are then known to be initialised)
+    __syncwarp();
+    if (cluster_reduce) cluster_arrive();
+    if (lane == 0) {
+      const int pre = n_groups < stages ? n_groups : stages;
       for (int g = pre; g < n_groups; ++g) {
         const int s = g % stages;
         if (!mbar_wait(&w_empty[s], ((g / stages) & 1) ^ 1)) break;
@@ -600,6 +610,7 @@ linear_tcgen05_skinny3d_kernel(const __grid_constant__ CUtensorMap map_a, const 
       }
     }
   } else if (warp == 1) {
+    if (cluster_reduce) cluster_arrive();
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc<MB>();
       bool ok = mbar_wait(a_full, 0);
@@ -627,19 +638,51 @@ linear_tcgen05_skinny3d_kernel(const __grid_constant__ CUtensorMap map_a, const 
     const int quarter = warp & 3;
     const int n = n0 + quarter * 32 + lane;
     float b = 0.f;
-    if (blockIdx.y == 0 && bias != nullptr && n < N) b = load_param(bias, n, bias_f32);
+    if ((blockIdx.y == 0 || cluster_reduce) && bias != nullptr && n < N) b = load_param(bias, n, bias_f32);
+    if (cluster_reduce) cluster_arrive();
     pdl_wait();
     const bool ok = mbar_wait(tmem_full_bar, 0);
     tc_fence_after();
-    if (ok && cluster_reduce) {
-      // K is split over the CTAs of a thread-block cluster: this CTA's partial sums go to its shared memory
+    if (cluster_reduce) {
+      // K is split over the CTAs of a thread-block cluster.  Row m is summed by CTA m % z: every CTA writes its
+      // partial sums of that row into THAT CTA's shared memory and arrives on its barrier; the owner waits for
+      // all of them, adds them in rank order, applies bias and activation and stores.  One one-way trip through
+      // the cluster's network; no CTA reads another's memory, so none has to wait for the others before it exits.
+      const int z = (int)gridDim.y, rank = (int)blockIdx.y;
+      const int rows_max = (MB + z - 1) / z;
       const int n_local = quarter * 32 + lane;
+      if (ok) {
 #pragma unroll 1
-      for (int c = 0; c < MB; c += 16) {
-        float v[16];
-        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, v);
+        for (int c = 0; c < MB; c += 16) {
+          float v[16];
+          tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, v);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) red_sh[(c + j) * BM + n_local] = v[j];
+          for (int j = 0; j < 16; ++j) part_sh[(c + j) * BM + n_local] = v[j];
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");          // the four epilogue warps: the rows are whole
+      cluster_wait();
+      for (int idx = (warp - 2) * 32 + lane; idx < M * (BM / 4); idx += 128) {
+        const int m = idx / (BM / 4), col = (idx % (BM / 4)) * 4;
+        const float4 v = *reinterpret_cast<const float4*>(&part_sh[m * BM + col]);
+        st_cluster_f32x4(&recv_sh[((size_t)rank * rows_max + m / z) * BM + col], (unsigned)(m % z), v);
+      }
+      __syncwarp();
+      if (lane < z) mbar_arrive_cluster(recv_bar, (unsigned)lane);
+      bool got = false;
+      for (uint32_t i = 0; i < WAIT_LIMIT && !got; ++i) got = mbar_try_wait_cluster(recv_bar, 0);
+      if (!got && lane == 0) atomicAdd(&g_wait_timeouts, 1);
+      if (got && n < N) {
+        for (int m = rank; m < M; m += z) {
+          float t = b;
+          for (int src = 0; src < z; ++src) t += recv_sh[((size_t)src * rows_max + m / z) * BM + n_local];
+          if (EPI == EPI_GELU_TANH) t = gelu_tanh_fast(t);
+          if (EPI == EPI_GELU_ERF) t = gelu_erf(t);
+          const int64_t o = (int64_t)m * ldo + n;
+          if (EPI == EPI_STORE_F32) reinterpret_cast<float*>(out)[o] = t;
+          else if (EPI == EPI_RESIDUAL) reinterpret_cast<float*>(out)[o] += t;
+          else reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(t);
+        }
       }
     } else if (ok) {
       const bool atomic = gridDim.y > 1;
@@ -671,38 +714,6 @@ linear_tcgen05_skinny3d_kernel(const __grid_constant__ CUtensorMap map_a, const 
     }
   }
 
-  if (cluster_reduce) {
-    // the cluster meets; its CTAs share the rows out, and each adds its rows' partial sums from all CTAs (its
-    // own included, in rank order) through distributed shared memory, applies bias and activation and stores;
-    // a second meeting keeps every CTA's memory alive until all have read it
-    __syncwarp();
-    cluster_sync_all();
-    if (warp >= 2) {
-      // row m is summed by CTA m % (cluster size): every CTA reads one row's partial sums from all of them
-      const int n_local = (warp & 3) * 32 + lane;
-      const int n = n0 + n_local;
-      const int z = (int)gridDim.y;
-      if (n < N) {
-        const float b = bias != nullptr ? load_param(bias, n, bias_f32) : 0.f;
-        for (int m = (int)blockIdx.y; m < M; m += z) {
-          float part[8];
-#pragma unroll
-          for (int rk = 0; rk < 8; ++rk) part[rk] = rk < z ? ld_cluster_f32(&red_sh[m * BM + n_local], (unsigned)rk) : 0.f;
-          float t = b;
-#pragma unroll
-          for (int rk = 0; rk < 8; ++rk) t += part[rk];
-          if (EPI == EPI_GELU_TANH) t = gelu_tanh_fast(t);
-          if (EPI == EPI_GELU_ERF) t = gelu_erf(t);
-          const int64_t o = (int64_t)m * ldo + n;
-          if (EPI == EPI_STORE_F32) reinterpret_cast<float*>(out)[o] = t;
-          else if (EPI == EPI_RESIDUAL) reinterpret_cast<float*>(out)[o] += t;
-          else reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(t);
-        }
-      }
-    }
-    __syncwarp();
-    cluster_sync_all();
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -1285,11 +1296,12 @@ KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, c
       const size_t a_bytes = (size_t)kb_per_split * mb * BK * 2;
       const size_t stage_bytes = (size_t)W_GROUP * BM * BK * 2;
       const int groups = (kb_per_split + W_GROUP - 1) / W_GROUP;
-      if (a_bytes + stage_bytes + 2048 + (size_t)mb * BM * 4 <= (size_t)SMEM_BUDGET && kb_per_split <= 256) {
-        int stages3 = (int)(((size_t)SMEM_BUDGET - a_bytes - 2048 - (size_t)mb * BM * 4) / stage_bytes);
+      const size_t recv_bytes = (size_t)(2 * mb + 8) * BM * 4 + 16;  // partial sums received from the cluster's CTAs, and this CTA's own
+      if (a_bytes + stage_bytes + 2048 + recv_bytes <= (size_t)SMEM_BUDGET && kb_per_split <= 256) {
+        int stages3 = (int)(((size_t)SMEM_BUDGET - a_bytes - 2048 - recv_bytes) / stage_bytes);
         if (stages3 > groups) stages3 = groups;
         if (stages3 > 3) stages3 = 3;
-        const size_t smem3 = a_bytes + (size_t)stages3 * stage_bytes + (2 * stages3 + 2) * 8 + 16 + 16 + (size_t)mb * BM * 4 + 1024;
+        const size_t smem3 = a_bytes + (size_t)stages3 * stage_bytes + (2 * stages3 + 2) * 8 + 16 + 16 + recv_bytes + 1024;
         CUtensorMap ma3, mw3;
         int rc3 = tensor_map_3d(A, lda, M, K, mb, kb_per_split, &ma3);
         if (rc3 != KVAD_OK) return rc3;

@@ -337,6 +337,8 @@ attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(base + (size_t)STAGES * D::STAGE_BYTES);
   uint64_t* empty_bar = full_bar + STAGES;
   __shared__ __align__(16) float acc_sh[TMA_CONSUMER_WARPS][HD];
+  __shared__ __align__(16) float recv_sh[8][HD + 4];         // cluster merge: the other splits' partial results arrive here
+  __shared__ uint64_t merge_bar;
   __shared__ float ml_sh[TMA_CONSUMER_WARPS][2];
   __shared__ int last_flag;
 
@@ -363,10 +365,14 @@ attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict
       dec_mbar_init(&full_bar[s], 1);
       dec_mbar_init(&empty_bar[s], TMA_CONSUMER_WARPS);
     }
+    dec_mbar_init(&merge_bar, n_splits > 1 ? n_splits - 1 : 1);     // the other splits' CTAs arrive here (cluster merge)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   __syncthreads();
+  // (cluster merge: every thread of the cluster arrives at its barrier now; the CTAs that later write into the
+  // first one's shared memory wait on it just before they do, by when its merge barrier is known to be initialised)
+  if (n_splits > 1 && cluster_merge) cluster_arrive();
 
   const int c = lane % CH, kl = lane / CH;
   float acc[8];
@@ -552,51 +558,60 @@ attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict
     total += ml_sh[w][1] * wscale[w];
   }
   if (n_splits > 1 && cluster_merge) {
-    // The splits of this (row, head) are the CTAs of one thread-block cluster: each leaves its partial in
-    // its own shared memory, the cluster meets, and the first CTA reads the others' through distributed
-    // shared memory.  No trip to global memory, no fence, no counter.
-    __shared__ float part_sh[HD + 2];
+    // The splits of this (row, head) are the CTAs of one thread-block cluster.  Every CTA but the first writes
+    // its partial result (unnormalised output, maximum, sum) into the FIRST one's shared memory and arrives on
+    // its barrier, then is done; the first waits for them and merges.  One one-way trip through the cluster's
+    // network: no trip to global memory, no CTA reads another's memory, nobody waits for a closing barrier.
+    if (split != 0) {
+      cluster_wait();
+      for (int d = tid; d < HD; d += TMA_THREADS) {
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < TMA_CONSUMER_WARPS; ++w) o += acc_sh[w][d] * wscale[w];
+        st_cluster_f32(&recv_sh[split][d], 0u, o);
+      }
+      if (tid == 0) {
+        st_cluster_f32(&recv_sh[split][HD], 0u, m);
+        st_cluster_f32(&recv_sh[split][HD + 1], 0u, total);
+      }
+      __syncthreads();                         // every thread's writes come before the one arrival
+      if (tid == 0) mbar_arrive_cluster(&merge_bar, 0u);
+      return;
+    }
+    bool got = false;
+    for (uint32_t i = 0; i < DEC_WAIT_LIMIT && !got; ++i) got = mbar_try_wait_cluster(&merge_bar, 0);
+    if (!got) {
+      if (tid == 0) atomicAdd(&g_decode_timeouts, 1);
+      return;
+    }
+    float ms[8], ws[8];
+    ms[0] = m;
+    ws[0] = total;
+#pragma unroll
+    for (int s2 = 1; s2 < 8; ++s2) {
+      ms[s2] = s2 < n_splits ? recv_sh[s2][HD] : -INFINITY;
+      ws[s2] = s2 < n_splits ? recv_sh[s2][HD + 1] : 0.f;
+    }
+    float gm = -INFINITY;
+#pragma unroll
+    for (int s2 = 0; s2 < 8; ++s2) gm = fmaxf(gm, ms[s2]);
+    float gl = 0.f;
+#pragma unroll
+    for (int s2 = 0; s2 < 8; ++s2) {
+      const float a = ms[s2] == -INFINITY ? 0.f : exp_for<T>(ms[s2] - gm);
+      gl += ws[s2] * a;                   // (the sum in rank order)
+      ws[s2] = a;
+    }
+    const float inv = 1.0f / gl;
     for (int d = tid; d < HD; d += TMA_THREADS) {
       float o = 0.f;
 #pragma unroll
       for (int w = 0; w < TMA_CONSUMER_WARPS; ++w) o += acc_sh[w][d] * wscale[w];
-      part_sh[d] = o;
+      o *= ws[0];
+#pragma unroll
+      for (int s2 = 1; s2 < 8; ++s2) o += (s2 < n_splits ? recv_sh[s2][d] : 0.f) * ws[s2];
+      out[(int64_t)r * ld_out + (int64_t)h * HD + d] = from_f32<T>(o * inv);
     }
-    if (tid == 0) {
-      part_sh[HD] = m;
-      part_sh[HD + 1] = total;
-    }
-    cluster_sync_all();
-    if (split == 0) {
-      // (every load is issued before the first is used: one trip through the cluster's network per phase)
-      float ms[8], ws[8];
-#pragma unroll
-      for (int s2 = 0; s2 < 8; ++s2) {
-        ms[s2] = s2 < n_splits ? ld_cluster_f32(&part_sh[HD], (unsigned)s2) : -INFINITY;
-        ws[s2] = s2 < n_splits ? ld_cluster_f32(&part_sh[HD + 1], (unsigned)s2) : 0.f;
-      }
-      float gm = -INFINITY;
-#pragma unroll
-      for (int s2 = 0; s2 < 8; ++s2) gm = fmaxf(gm, ms[s2]);
-      float gl = 0.f;
-#pragma unroll
-      for (int s2 = 0; s2 < 8; ++s2) {
-        const float a = ms[s2] == -INFINITY ? 0.f : exp_for<T>(ms[s2] - gm);
-        gl += ws[s2] * a;                 // (the sum in rank order, as before)
-        ws[s2] = a;
-      }
-      const float inv = 1.0f / gl;
-      for (int d = tid; d < HD; d += TMA_THREADS) {
-        float v[8];
-#pragma unroll
-        for (int s2 = 0; s2 < 8; ++s2) v[s2] = s2 < n_splits ? ld_cluster_f32(&part_sh[d], (unsigned)s2) : 0.f;
-        float o = 0.f;
-#pragma unroll
-        for (int s2 = 0; s2 < 8; ++s2) o += v[s2] * ws[s2];
-        out[(int64_t)r * ld_out + (int64_t)h * HD + d] = from_f32<T>(o * inv);
-      }
-    }
-    cluster_sync_all();          // nobody's shared memory goes away while the first CTA reads it
     return;
   }
   float* part = n_splits > 1 ? scratch + (((int64_t)r * n_heads + h) * n_splits + split) * (HD + 2) : nullptr;

@@ -296,6 +296,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       }
       tc_fence_after();
       const bool add_bias = z == 0;
+      const float bias_on = add_bias ? 1.f : 0.f;     // only the first share of K brings the bias (staged values are finite)
       const bool atomic = n_splits > 1;
       // two warps share a quarter of the lanes: the first takes the left half of the columns, the second the right
       constexpr int HALF = BN >= 32 ? BN / 2 : BN;
@@ -321,7 +322,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             tmem_ld16(acc + (uint32_t)(c0 + cc), v);
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              float x = v[j] + (add_bias ? bias_sh[c0 + cc + j] : 0.f);
+              float x = fmaf(bias_sh[c0 + cc + j], bias_on, v[j]);     // (no test per element: see bias_on)
               if (EPI == EPI_GELU_TANH) x = gelu_tanh_fast(x);
               if (EPI == EPI_GELU_ERF) x = gelu_erf(x);
               v[j] = x;

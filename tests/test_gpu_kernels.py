@@ -430,6 +430,54 @@ def _decode_split_case(ops, g, dtype, hd, n_heads, n_kv, window):
     assert int(ops._counters.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hd,n_heads,n_kv,window", [(64, 12, 12, 0), (128, 8, 2, 0), (32, 10, 5, 100), (256, 12, 12, 0)])
+def test_attention_decode_many_pairs(dtype, hd, n_heads, n_kv, window):
+    """More (row, head) pairs than CTAs fit the GPU at once (the grid runs in waves), with sequences of very unequal
+    length: what the reference gives, the same bits on a second launch, and the step's own keys and values taken
+    from the projection's output and written to the cache."""
+    from kvad_b200.ops import decode_force_plain, decode_wait_timeouts
+    g = torch.Generator().manual_seed(11 * hd + n_heads)
+    ops = Ops(DT[dtype])
+    n_rows = 460 // n_heads + 3
+    lens = [int(x) for x in torch.randint(1, 330, (n_rows,), generator=g)]
+    lens[0], lens[1], lens[2] = 1, 64, 65
+    table, kp, vp, ks, vs = make_cache(g, dtype, n_rows, lens, n_kv, hd)
+    row_seq = torch.arange(n_rows, dtype=torch.int32)
+    row_pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32)
+    q = torch.randn(n_rows, n_heads * hd, generator=g).to(DT[dtype])
+    scale = 0.9 / math.sqrt(hd)
+    ref = attention_ref(q, ks, vs, row_seq, row_pos, n_heads, scale, window)
+    outs = []
+    for mode in (0, 0):
+        decode_force_plain(mode)
+        try:
+            out = torch.full((n_rows, n_heads * hd), float("nan"), device="cuda", dtype=DT[dtype])
+            ops.attention_decode(dev(q), out, dev(row_seq), dev(row_pos), dev(table), dev(kp), dev(vp), n_heads, scale, window)
+        finally:
+            decode_force_plain(0)
+        assert rel(out, ref) < KTOL[dtype], mode
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])             # the same bits every time
+    # with the step's own keys and values handed in (and written to the cache by the kernel)
+    kn = torch.stack([ks[s][l - 1].reshape(-1) for s, l in enumerate(lens)]).to(DT[dtype])
+    vn = torch.stack([vs[s][l - 1].reshape(-1) for s, l in enumerate(lens)]).to(DT[dtype])
+    kp2, vp2 = kp.clone(), vp.clone()
+    for s, l in enumerate(lens):
+        kp2[table[s, (l - 1) // 64], :, (l - 1) % 64] = float("nan")
+        vp2[table[s, (l - 1) // 64], :, (l - 1) % 64] = float("nan")
+    kp_d, vp_d = dev(kp2), dev(vp2)
+    new = torch.cat([kn, vn], dim=1).cuda()
+    w = n_kv * hd
+    out = torch.full((n_rows, n_heads * hd), float("nan"), device="cuda", dtype=DT[dtype])
+    ops.attention_decode(dev(q), out, dev(row_seq), dev(row_pos), dev(table), kp_d, vp_d, n_heads, scale, window,
+                         k_new=new[:, :w], v_new=new[:, w:])
+    assert rel(out, ref) < KTOL[dtype]
+    same = lambda a, b: torch.equal(torch.nan_to_num(a.float().cpu(), nan=7.0), torch.nan_to_num(b.float(), nan=7.0))
+    assert same(kp_d, kp) and same(vp_d, vp)
+    assert decode_wait_timeouts() == 0
+
+
 def test_attention_decode_finds_one_far_key():
     g = torch.Generator().manual_seed(19)
     ops = Ops(torch.bfloat16)

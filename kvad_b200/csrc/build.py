@@ -31,6 +31,7 @@ _FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-st
 LIBRARIES = ("rows", "linear_simt", "attention_simt", "sampling", "linear_tcgen05", "linear_rows",
              "attention_prefill", "attention_decode")
 
+_registered: dict[str, str] = {}       # kernel sources from outside the package: name -> path of the .cu file
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
 _dir_lock = threading.Lock()
@@ -82,15 +83,37 @@ def _find_build_dir() -> str:
     raise BuildError(f"no writable folder for compiled kernels (tried {candidates})")
 
 
+def register_source(name: str, path: str) -> None:
+    """A kernel source from outside the package (a part that brings its own kernel): compiled with
+    the same flags and with this folder on the include path, kept in the same build folder."""
+    if name in LIBRARIES:
+        raise BuildError(f"`{name}` is one of the package's own kernel libraries")
+    path = os.path.abspath(path)
+    if not os.path.isfile(path):
+        raise BuildError(f"no kernel source {path}")
+    with _lock:
+        if _registered.get(name) not in (None, path):
+            _loaded.pop(name, None)
+        _registered[name] = path
+
+
+def registered_sources() -> dict[str, str]:
+    return dict(_registered)
+
+
+def _source_path(name: str) -> str:
+    return _registered.get(name) or os.path.join(_HERE, name + ".cu")
+
+
 def sources() -> list[str]:
-    return [n for n in LIBRARIES if os.path.isfile(os.path.join(_HERE, n + ".cu"))]
+    return [n for n in LIBRARIES if os.path.isfile(os.path.join(_HERE, n + ".cu"))] + list(_registered)
 
 
 def _digest(name: str) -> str:
     h = hashlib.sha256()
     headers = sorted(fn for fn in os.listdir(_HERE) if fn.endswith((".cuh", ".h")))
-    for fn in (name + ".cu", *headers):
-        with open(os.path.join(_HERE, fn), "rb") as f:
+    for fn in (_source_path(name), *(os.path.join(_HERE, x) for x in headers)):
+        with open(fn, "rb") as f:
             h.update(f.read())
     h.update(" ".join(_FLAGS).encode())
     return h.hexdigest()[:16]
@@ -102,7 +125,7 @@ def library_path(name: str) -> str:
 
 def compile_library(name: str, *, verbose: bool = True) -> str:
     """Builds one library if it is not built yet; returns its path."""
-    src = os.path.join(_HERE, name + ".cu")
+    src = _source_path(name)
     if not os.path.isfile(src):
         raise BuildError(f"no kernel source {src}")
     target = library_path(name)
@@ -112,7 +135,7 @@ def compile_library(name: str, *, verbose: bool = True) -> str:
     tmp = f"{target}.{os.getpid()}.{threading.get_ident()}.tmp"
     cmd = [nvcc, *_FLAGS, "-I", _HERE, "-o", tmp, src]
     if verbose:
-        _say(f"compiling {name}.cu for sm_100a ...")
+        _say(f"compiling {os.path.basename(src)} for sm_100a ...")
     t0 = time.time()
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, cwd=_HERE)
     done = threading.Event()

@@ -725,220 +725,6 @@ linear_tcgen05_skinny3d_kernel(const __grid_constant__ CUtensorMap map_a, const 
 }
 
 // ---------------------------------------------------------------------------------------------
-// The swapped form with the norm in front of it fused in: out = epi(LayerNorm(x[rows]) . W^T + b).
-// The four epilogue warps first normalise the (at most 16) rows of the 32-bit residual stream -
-// mean, biased variance (two passes over a row held in registers), 1/sqrt(var+eps), gain and bias,
-// all in 32-bit - round to bfloat16 and write them into shared memory in exactly the layout TMA's
-// 128-byte swizzle would have produced (16-byte chunk index XOR row-in-group), for every 64-wide
-// block of K at once.  Meanwhile the producer streams the weights (all requested before the
-// dependent-launch wait).  The MMA warp waits for "activations ready", then runs down K.  The
-// normalised rows never reach global memory and one launch per norm disappears.
-// No split over K: the epilogues here are the storing ones (qkv; up-projection + GELU; logits).
-// ---------------------------------------------------------------------------------------------
-template <int MB, int EPI, int NI>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-linear_tcgen05_ln_kernel(const __grid_constant__ CUtensorMap map_w, const float* __restrict__ x, int64_t ldx,
-                         const int* __restrict__ row_index, const void* __restrict__ gain,
-                         const void* __restrict__ beta, int params_f32, float eps,
-                         const void* __restrict__ bias, int bias_f32, void* __restrict__ out, int64_t ldo,
-                         int M, int N, int K, int stages) {
-  constexpr uint32_t W_BYTES = BM * BK * 2;
-  constexpr uint32_t A_BYTES = MB * BK * 2;            // one 64-wide block of the normalised rows
-  constexpr int TMEM_COLS = MB < 32 ? 32 : MB;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  const int num_kb = (K + BK - 1) / BK;
-  uint8_t* a_tiles = smem;                                         // num_kb blocks, resident
-  uint8_t* w_tiles = smem + (size_t)num_kb * A_BYTES;              // ring of `stages`
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(w_tiles + (size_t)stages * W_BYTES);
-  uint64_t* empty_bar = full_bar + stages;
-  uint64_t* a_ready_bar = empty_bar + stages;
-  uint64_t* tmem_full_bar = a_ready_bar + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BM;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
-    }
-    mbar_init(a_ready_bar, 128);
-    mbar_init(tmem_full_bar, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  pdl_launch_dependents();
-  if (warp == 0) {
-    if (lane == 0) {
-      for (int i = 0; i < num_kb; ++i) {
-        const int s = i % stages;
-        if (i >= stages && !mbar_wait(&empty_bar[s], ((i / stages) & 1) ^ 1)) break;
-        mbar_expect_tx(&full_bar[s], W_BYTES);
-        tma_load_2d(w_tiles + (size_t)s * W_BYTES, &map_w, &full_bar[s], i * BK, n0);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc<MB>();
-      bool ok = mbar_wait(a_ready_bar, 0);
-      for (int i = 0; i < num_kb && ok; ++i) {
-        const int s = i % stages;
-        ok = mbar_wait(&full_bar[s], (i / stages) & 1);
-        if (!ok) break;
-        tc_fence_after();
-        const uint64_t w_desc = sw128_desc(smem_u32(w_tiles + (size_t)s * W_BYTES));
-        const uint64_t a_desc = sw128_desc(smem_u32(a_tiles + (size_t)i * A_BYTES));
-#pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k)
-          umma(tmem_base, w_desc + (uint64_t)(k * 2), a_desc + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
-        umma_commit(&empty_bar[s]);
-      }
-      umma_commit(tmem_full_bar);
-    }
-  } else {
-    // ---- the norm, by the four epilogue warps: warp e takes rows e, e+4, ...  A row is read from
-    // memory once, into registers (NI chunks of 8 per lane), and RB rows are in flight together.
-    const int e = warp - 2;
-    const int k_padded = num_kb * BK;
-    constexpr int RB = NI <= 4 ? 4 : 2;
-    // the norm's parameters and the row list are not the previous kernel's work: they are staged in
-    // shared memory (behind the barriers) before the dependent-launch wait
-    float* gain_sh = reinterpret_cast<float*>(tmem_slot + 4);
-    float* beta_sh = gain_sh + k_padded;
-    for (int k = threadIdx.x - 64; k < k_padded; k += 128) {
-      gain_sh[k] = k < K ? load_param(gain, k, params_f32) : 0.f;
-      beta_sh[k] = (k < K && beta) ? load_param(beta, k, params_f32) : 0.f;
-    }
-    int src_row[RB * (MB / 4 / RB)];
-#pragma unroll
-    for (int j = 0; j < MB / 4; ++j) {
-      const int m = e + 4 * j;
-      src_row[j] = (m < M) ? (row_index ? row_index[m] : m) : 0;
-    }
-    asm volatile("bar.sync 1, 128;" ::: "memory");      // the four norm warps only
-    pdl_wait();
-    for (int jb = 0; jb < MB / 4; jb += RB) {
-      float v[RB][NI][8];
-#pragma unroll
-      for (int r = 0; r < RB; ++r) {
-        const int m = e + 4 * (jb + r);
-        const float* xr = x + (int64_t)src_row[jb + r] * ldx;
-#pragma unroll
-        for (int i = 0; i < NI; ++i) {
-          const int k0 = (lane + 32 * i) * 8;
-          if (m < M && k0 < K) {
-            const float4 a = *reinterpret_cast<const float4*>(xr + k0), b = *reinterpret_cast<const float4*>(xr + k0 + 4);
-            v[r][i][0] = a.x; v[r][i][1] = a.y; v[r][i][2] = a.z; v[r][i][3] = a.w;
-            v[r][i][4] = b.x; v[r][i][5] = b.y; v[r][i][6] = b.z; v[r][i][7] = b.w;
-          } else {
-#pragma unroll
-            for (int t = 0; t < 8; ++t) v[r][i][t] = 0.f;
-          }
-        }
-      }
-      float mean[RB], inv[RB];
-#pragma unroll
-      for (int r = 0; r < RB; ++r) {
-        float sum = 0.f;
-#pragma unroll
-        for (int i = 0; i < NI; ++i)
-#pragma unroll
-          for (int t = 0; t < 8; ++t) sum += v[r][i][t];
-        mean[r] = warp_sum(sum) / (float)K;
-        float sq = 0.f;
-#pragma unroll
-        for (int i = 0; i < NI; ++i) {
-          if ((lane + 32 * i) * 8 < K) {
-#pragma unroll
-            for (int t = 0; t < 8; ++t) {
-              const float d = v[r][i][t] - mean[r];
-              sq = fmaf(d, d, sq);
-            }
-          }
-        }
-        inv[r] = 1.0f / sqrtf(warp_sum(sq) / (float)K + eps);
-      }
-#pragma unroll
-      for (int i = 0; i < NI; ++i) {
-        const int k0 = (lane + 32 * i) * 8;
-        if (k0 >= k_padded) continue;
-        float gn[8], bt[8];
-        {
-          const float4 g0 = *reinterpret_cast<const float4*>(gain_sh + k0), g1 = *reinterpret_cast<const float4*>(gain_sh + k0 + 4);
-          const float4 b0 = *reinterpret_cast<const float4*>(beta_sh + k0), b1 = *reinterpret_cast<const float4*>(beta_sh + k0 + 4);
-          gn[0] = g0.x; gn[1] = g0.y; gn[2] = g0.z; gn[3] = g0.w; gn[4] = g1.x; gn[5] = g1.y; gn[6] = g1.z; gn[7] = g1.w;
-          bt[0] = b0.x; bt[1] = b0.y; bt[2] = b0.z; bt[3] = b0.w; bt[4] = b1.x; bt[5] = b1.y; bt[6] = b1.z; bt[7] = b1.w;
-        }
-        const int kb = k0 >> 6, chunk = (k0 & 63) >> 3;
-#pragma unroll
-        for (int r = 0; r < RB; ++r) {
-          const int m = e + 4 * (jb + r);
-          uint4 packed = make_uint4(0u, 0u, 0u, 0u);
-          if (m < M && k0 < K) {
-            float y[8];
-#pragma unroll
-            for (int t = 0; t < 8; ++t) y[t] = (v[r][i][t] - mean[r]) * inv[r] * gn[t] + bt[t];
-            __nv_bfloat162 p0 = __floats2bfloat162_rn(y[0], y[1]), p1 = __floats2bfloat162_rn(y[2], y[3]);
-            __nv_bfloat162 p2 = __floats2bfloat162_rn(y[4], y[5]), p3 = __floats2bfloat162_rn(y[6], y[7]);
-            packed.x = *reinterpret_cast<uint32_t*>(&p0); packed.y = *reinterpret_cast<uint32_t*>(&p1);
-            packed.z = *reinterpret_cast<uint32_t*>(&p2); packed.w = *reinterpret_cast<uint32_t*>(&p3);
-          }
-          uint8_t* row_base = a_tiles + (size_t)(m >> 3) * 1024 + (size_t)(m & 7) * 128;
-          *reinterpret_cast<uint4*>(row_base + (size_t)kb * A_BYTES + (size_t)((chunk ^ (m & 7)) << 4)) = packed;
-        }
-      }
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // these stores are read by the tensor core
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(a_ready_bar)) : "memory");
-
-    // ---- the epilogue
-    const int quarter = warp & 3;
-    const int n = n0 + quarter * 32 + lane;
-    const bool ok = mbar_wait(tmem_full_bar, 0);
-    tc_fence_after();
-    if (ok) {
-      float b = 0.f;
-      if (bias != nullptr && n < N) b = load_param(bias, n, bias_f32);
-#pragma unroll 1
-      for (int c = 0; c < MB; c += 16) {
-        float v[16];
-        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, v);
-        if (n < N && c < M) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = c + j;
-            if (m < M) {
-              float t = v[j] + b;
-              if (EPI == EPI_GELU_TANH) t = gelu_tanh_fast(t);
-              if (EPI == EPI_GELU_ERF) t = gelu_erf(t);
-              const int64_t o = (int64_t)m * ldo + n;
-              if (EPI == EPI_STORE_F32) reinterpret_cast<float*>(out)[o] = t;
-              else reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(t);
-            }
-          }
-        }
-      }
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  if (warp == 1) {
-    __syncwarp();
-    tmem_dealloc(tmem_base, TMEM_COLS);
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
 // Host side: tensor maps (made once per tensor and shape, then reused) and the launch.
 // ---------------------------------------------------------------------------------------------
 struct MapKey {
@@ -1164,71 +950,7 @@ int launch_skinny3d_epi(int epilogue, const CUtensorMap& ma, const CUtensorMap& 
   KVAD_FAIL(KVAD_ERR_ARGUMENT, "linear_tcgen05: unknown epilogue %d", epilogue);
 }
 
-template <int MB, int EPI, int NI>
-int launch_ln(const CUtensorMap& mw, const float* x, int64_t ldx, const int* row_index, const void* gain, const void* beta,
-              int params_f32, float eps, const void* bias, int bias_f32, void* out, int64_t ldo, int M, int N, int K,
-              int stages, size_t smem, cudaStream_t stream) {
-  static size_t configured = 0;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(linear_tcgen05_ln_kernel<MB, EPI, NI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "linear_tcgen05_ln: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    configured = smem;
-  }
-  kvad_launch(linear_tcgen05_ln_kernel<MB, EPI, NI>, dim3((N + BM - 1) / BM), dim3(NUM_THREADS), smem, stream, mw, x, ldx,
-              row_index, gain, beta, params_f32, eps, bias, bias_f32, out, ldo, M, N, K, stages);
-  KVAD_CHECK_LAUNCH("linear_tcgen05_ln");
-  return KVAD_OK;
-}
-
-template <int MB, int NI>
-int launch_ln_epi(int epilogue, const CUtensorMap& mw, const float* x, int64_t ldx, const int* row_index, const void* gain,
-                  const void* beta, int params_f32, float eps, const void* bias, int bias_f32, void* out, int64_t ldo,
-                  int M, int N, int K, int stages, size_t smem, cudaStream_t stream) {
-  switch (epilogue) {
-    case EPI_STORE: return launch_ln<MB, EPI_STORE, NI>(mw, x, ldx, row_index, gain, beta, params_f32, eps, bias, bias_f32, out, ldo, M, N, K, stages, smem, stream);
-    case EPI_GELU_TANH: return launch_ln<MB, EPI_GELU_TANH, NI>(mw, x, ldx, row_index, gain, beta, params_f32, eps, bias, bias_f32, out, ldo, M, N, K, stages, smem, stream);
-    case EPI_GELU_ERF: return launch_ln<MB, EPI_GELU_ERF, NI>(mw, x, ldx, row_index, gain, beta, params_f32, eps, bias, bias_f32, out, ldo, M, N, K, stages, smem, stream);
-    case EPI_STORE_F32: return launch_ln<MB, EPI_STORE_F32, NI>(mw, x, ldx, row_index, gain, beta, params_f32, eps, bias, bias_f32, out, ldo, M, N, K, stages, smem, stream);
-  }
-  KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "linear_tcgen05_ln: epilogue %d does not go with a fused norm", epilogue);
-}
-
 }  // namespace
-
-// out = epilogue(LayerNorm(x[row_index]) . W^T + bias) for at most 16 rows of at most 2048 columns, the norm computed inside
-// the kernel.  x: the 32-bit residual stream with row stride ldx; row_index: which rows (or null: the
-// first M); gain / beta (beta may be null): the norm's parameters, 32-bit if params_f32 else bfloat16.
-// Refuses (KVAD_ERR_UNSUPPORTED) more rows or columns or a residual epilogue; the caller then
-// normalises separately.  (With more rows every CTA would spend longer normalising than a kernel of
-// its own takes.)
-KVAD_EXPORT int kvad_linear_tcgen05_ln(const float* x, int64_t ldx, const int* row_index, const void* gain,
-                                       const void* beta, int params_f32, float eps, const void* W, const void* bias,
-                                       int bias_f32, void* out, int64_t ldo, int M, int N, int K, int epilogue,
-                                       cudaStream_t stream) {
-  KVAD_REQUIRE(M >= 0 && N > 0 && K > 0 && gain != nullptr, "linear_tcgen05_ln: bad sizes M=%d N=%d K=%d", M, N, K);
-  if (M > 16 || K > 2048) KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "linear_tcgen05_ln: %d rows of %d columns are more than the 16 x 2048 this form takes", M, K);
-  if (K % 8 != 0 || ldx % 4 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
-    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "linear_tcgen05_ln: K=%d must be a multiple of 8 and the operands 16-byte aligned", K);
-  KVAD_REQUIRE(ldx >= K && ldo >= N, "linear_tcgen05_ln: leading dimensions ldx=%lld ldo=%lld too small", (long long)ldx, (long long)ldo);
-  if (M == 0) return KVAD_OK;
-  const int mb = 16;
-  const int num_kb = (K + BK - 1) / BK;
-  const size_t a_bytes = (size_t)num_kb * mb * BK * 2;
-  const size_t params_bytes = (size_t)num_kb * BK * 2 * sizeof(float) + 32;     // the norm's gain and bias, staged
-  const size_t fixed = a_bytes + params_bytes + 1024 + 64 + 16 * 32;
-  if (fixed + 4 * (size_t)(BM * BK * 2) > (size_t)SMEM_BUDGET)
-    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "linear_tcgen05_ln: %d rows of width %d do not fit shared memory beside the weights", mb, K);
-  int stages = (int)(((size_t)SMEM_BUDGET - fixed) / (size_t)(BM * BK * 2));
-  if (stages > 12) stages = 12;
-  if (stages > num_kb) stages = num_kb;
-  const size_t smem = a_bytes + (size_t)stages * (BM * BK * 2) + (2 * stages + 2) * 8 + 16 + params_bytes + 1024;
-  CUtensorMap mw;
-  int rc = tensor_map(W, K, N, K, BM, &mw);
-  if (rc != KVAD_OK) return rc;
-  if (K <= 1024)
-    return launch_ln_epi<16, 4>(epilogue, mw, x, ldx, row_index, gain, beta, params_f32, eps, bias, bias_f32, out, ldo, M, N, K, stages, smem, stream);
-  return launch_ln_epi<16, 8>(epilogue, mw, x, ldx, row_index, gain, beta, params_f32, eps, bias, bias_f32, out, ldo, M, N, K, stages, smem, stream);
-}
 
 // `force` fixes what the kernel otherwise chooses (tests): bits 0-15 the tile width of the wide
 // form (16, 32, 64, 128, 192 or 256); bits 16-23 how many CTAs share K (residual epilogue only);

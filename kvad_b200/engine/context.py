@@ -128,25 +128,3 @@ class StepContext:
 
     def state(self, entry: int) -> torch.Tensor:
         return self.cache.state_view(entry)
-
-    def attend(self, q, k, v, out, view: KVView, n_heads: int, scale: float, writes_cache: bool = True) -> None:
-        """Writes the rows' keys and values to the cache entry (if this call owns it) and lets every row
-        attend over its sequence up to its own position.  Picks the kernels for this step's shape."""
-        ops, b = self.ops, self.batch
-        hd = view.k_pages.shape[-1]
-        if b.is_decode and ops.fast_decode and ops.decode_takes(hd):
-            splits = ops.decode_splits(self.n_rows, n_heads, view.page_table.shape[1])
-            scratch = self.buffer((self.n_rows * n_heads * splits * (hd + 2),), torch.float32) if splits > 1 else None
-            ops.attention_decode(q, out, self.row_seq, self.row_pos, view.page_table, view.k_pages, view.v_pages,
-                                 n_heads, scale, view.window or 0, n_splits=splits, scratch=scratch,
-                                 k_new=k if writes_cache else None, v_new=v if writes_cache else None,
-                                 merge_in_kernel=True)
-            return
-        if writes_cache:
-            ops.kv_store(k, v, self.row_seq, self.row_pos, view.page_table, view.k_pages, view.v_pages)
-        if (not b.is_decode) and ops.tensor_core_prefill and ops.prefill_takes(hd):
-            ops.attention_prefill(q, out, self.seq_starts, self.kv_lens, self.n_seqs, b.max_new, view.page_table,
-                                  view.k_pages, view.v_pages, n_heads, scale, view.window or 0)
-        else:
-            ops.attention(q, out, self.row_seq, self.row_pos, view.page_table, view.k_pages, view.v_pages,
-                          n_heads, scale, view.window or 0)

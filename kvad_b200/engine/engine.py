@@ -49,10 +49,20 @@ def parse_dtype(name) -> torch.dtype:
 
 
 class _SampleBuffers:
-    """Sampling options of a step's rows (pinned host + device) and the chosen tokens."""
+    """Sampling options of a step's rows (pinned host + device) and the chosen tokens.
+
+    The options go up through a ring of pinned staging buffers, each with an event recorded after
+    its copy was queued: a buffer is written again only once the copy that last read it has run.
+    The generation loop launches a step ahead of the one it waits for, so without the ring the host
+    could overwrite a step's uniform numbers before the device had fetched them."""
+
+    STAGES = 4
 
     def __init__(self, cap: int, device):
-        self.host = torch.zeros((4, cap), dtype=torch.float32).pin_memory()
+        self._hosts = [torch.zeros((4, cap), dtype=torch.float32).pin_memory() for _ in range(self.STAGES)]
+        self._events: list = [None] * self.STAGES
+        self._next = 0
+        self.cap = cap
         self.dev = torch.zeros((4, cap), dtype=torch.float32, device=device)
         self.out = torch.zeros(cap, dtype=torch.int32, device=device)
         self.out_host = torch.zeros(cap, dtype=torch.int32).pin_memory()
@@ -64,15 +74,23 @@ class _SampleBuffers:
         """Uploads temperature, top-p, this step's uniform draw and top-k per row; True if all rows are greedy."""
         if all(s.params.greedy for s in samplers):
             return True
-        h = self.host.numpy()
+        i = self._next
+        self._next = (i + 1) % self.STAGES
+        if self._events[i] is not None:
+            self._events[i].synchronize()
+        host = self._hosts[i]
+        h = host.numpy()
         hk = h[3].view(np.int32)
-        for i, s in enumerate(samplers):
-            h[0, i] = s.params.temperature
-            h[1, i] = s.params.top_p
-            h[2, i] = s.next_uniform()
-            hk[i] = s.params.top_k
-        self.dev.copy_(self.host, non_blocking=True)
-        engine.h2d_bytes += self.host.numel() * 4
+        for j, s in enumerate(samplers):
+            h[0, j] = s.params.temperature
+            h[1, j] = s.params.top_p
+            h[2, j] = s.next_uniform()
+            hk[j] = s.params.top_k
+        self.dev.copy_(host, non_blocking=True)
+        ev = self._events[i] or torch.cuda.Event()
+        ev.record()
+        self._events[i] = ev
+        engine.h2d_bytes += host.numel() * 4
         return False
 
     def read_async(self, n: int, engine) -> "_PendingTokens":
@@ -192,9 +210,10 @@ class Engine:
         return self.cache.length(slot)
 
     def room(self, prompt_len: int) -> int:
-        if self.max_positions is None:
-            return 1 << 30
-        return self.max_positions - prompt_len
+        """How many tokens still fit after a prompt of this length: up to the model's own bound, or,
+        for a model without one, up to what the whole cache holds."""
+        bound = self.max_positions if self.max_positions is not None else self.cache.max_tokens
+        return bound - prompt_len
 
     # -- the step ----------------------------------------------------------------------
     def _meta_for(self, n_rows: int, n_seqs: int) -> DeviceMeta:
@@ -255,7 +274,8 @@ class Engine:
         upload and one launch instead of a launch per kernel from the host."""
         ctx = self.begin_step(entries)
         b = ctx.batch
-        key = ("step", b.n_rows, b.n_seqs, b.max_new, ctx.n_want, id(ctx.meta), self.arena.generation)
+        key = ("step", b.n_rows, b.n_seqs, b.max_new, ctx.n_want, id(ctx.meta), self.arena.generation,
+               self.ops.path_key())
         logits = self._replay_or_run(key, lambda: self.model.forward(ctx))
         self.end_step(ctx)
         return logits
@@ -295,7 +315,7 @@ class Engine:
 
     # -- sampling on the device ----------------------------------------------------------
     def _sampling_buffers(self, n: int):
-        if self._sample_bufs is None or self._sample_bufs.host.shape[1] < n:
+        if self._sample_bufs is None or self._sample_bufs.cap < n:
             cap = max(64, 1 << (n - 1).bit_length())
             self._sample_bufs = _SampleBuffers(cap, self.device)
         return self._sample_bufs
@@ -351,7 +371,7 @@ class Engine:
         ctx = self.begin_step([StepEntry(slot, toks, (0,)) for slot, toks in entries], meta=plan.meta,
                               keep_tokens=device_fed)
         greedy = plan.bufs.load(samplers, self)
-        key = ("decode", n, greedy, id(plan.meta), self.arena.generation)
+        key = ("decode", n, greedy, id(plan.meta), self.arena.generation, self.ops.path_key())
         self._replay_or_run(key, lambda: self._decode_body(ctx, plan, greedy))
         self.end_step(ctx)
         return plan
@@ -394,6 +414,26 @@ class Engine:
         stats = run_all(self, reqs, batch_size or max(1, len(reqs)))
         outs = [r.generated for r in reqs]
         return (outs, stats) if return_stats else outs
+
+    # -- replay ------------------------------------------------------------------------------
+    def logits_replay(self, steps, out_dir: str) -> int:
+        """Feeds given tokens step by step and writes the wanted logits as `<out_dir>/<step>.f32`;
+        nothing is sampled.  `steps`: an iterable of trace records (dicts, or JSON lines) in the format
+        of `bin/trace_run`.  Returns the number of steps run."""
+        import json as _json
+
+        from .replay import Replayer
+        rep = Replayer(self, out_dir)
+        n = 0
+        for rec in steps:
+            if isinstance(rec, (str, bytes)):
+                if not rec.strip():
+                    continue
+                rec = _json.loads(rec)
+            rep.run_step(rec)
+            n += 1
+        rep.close_all()
+        return n
 
     # -- accounting --------------------------------------------------------------------------
     def describe(self) -> str:

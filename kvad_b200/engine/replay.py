@@ -68,10 +68,14 @@ class Replayer:
             self.run_step(record)
             print(f"done {record.get('step')}", file=out, flush=True)
             n += 1
+        self.close_all()
+        return n
+
+    def close_all(self) -> None:
+        """Gives back what requests still hold that no step has ended."""
         for slot in self.slots.values():
             self.engine.close(slot)
         self.slots.clear()
-        return n
 
 
 def main(argv=None) -> int:

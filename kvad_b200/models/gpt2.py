@@ -131,7 +131,7 @@ def plan(c: Gpt2Config) -> ModelPlan:
         order=ModelPlan.straight_order(c.n_layer),
         # stored causal masks and the like are buffers, not weights (crates/llm/src/weights.rs:716-721)
         ignored_suffixes=(".attn.bias", ".attn.masked_bias", "rotary_emb.inv_freq", "embeddings.position_ids"),
-        eos_token_ids=c.eos_token_ids,
+        eos_token_ids=c.eos_token_ids, max_positions=c.n_positions,
         summary=(f"gpt2 · {c.n_layer} layers · {c.n_head} heads{gqa} · {c.n_embd} embd · "
                  f"{c.n_positions} ctx · {c.vocab_size} vocab"),
     )

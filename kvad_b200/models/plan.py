@@ -41,6 +41,10 @@ class ModelPlan:
     ignored_suffixes: tuple[str, ...] = ()        # buffers in checkpoints that are not weights
     eos_token_ids: tuple[int, ...] = ()
     summary: str = ""
+    #: the longest sequence the model takes, whatever bounds it (a learned position table, the range a
+    #: rotary encoding was trained for, a configuration key); None: only the cache bounds a sequence.
+    #: A position table in the embedding bounds it too; the smaller of the two holds.
+    max_positions: Optional[int] = None
 
     @staticmethod
     def straight_order(n_layers: int) -> tuple[LayerCall, ...]:
@@ -80,7 +84,9 @@ class Model:
 
     @property
     def max_positions(self) -> Optional[int]:
-        return self.embedding.max_positions
+        """The longest sequence: the plan's own bound and the embedding's position table, whichever is smaller."""
+        bounds = [b for b in (self.plan.max_positions, getattr(self.embedding, "max_positions", None)) if b]
+        return min(bounds) if bounds else None
 
     @property
     def graph_safe(self) -> bool:

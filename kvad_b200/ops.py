@@ -53,8 +53,6 @@ _SIGNATURES = {
         "kvad_linear_tcgen05": [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int,
                                 c_int, c_int, c_void_p],
         "kvad_linear_tcgen05_status": [],
-        "kvad_linear_tcgen05_ln": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p,
-                                   c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p],
     },
     "linear_rows": {
         "kvad_linear_rows": [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int,
@@ -82,6 +80,32 @@ _SIGNATURES = {
 
 _bound: dict[str, ctypes.CDLL] = {}
 _pdl = os.environ.get("KVAD_PDL", "1") != "0"
+_switch_epoch = 0          # bumped by every switch that changes which kernels a step launches
+
+
+def register_kernels(name: str, source: str, signatures: dict) -> None:
+    """The door for a part that brings a kernel of its own: `source` is a `.cu` file anywhere (it may
+    include this package's `common.cuh`; it must contain `KVAD_DEFINE_LAST_ERROR()` once), `signatures`
+    maps its exported C entry points (returning 0 or a negative code, message through
+    `kvad_last_error`) to their ctypes argument lists.  Afterwards `lib(name)` compiles it for
+    sm_100a on first use and loads it like the package's own libraries; `launch(handle, status)`
+    turns a refusal into a `KernelError` and counts the launch."""
+    if name in _SIGNATURES and name not in build.registered_sources():
+        raise ValueError(f"`{name}` is one of the package's own kernel libraries")
+    build.register_source(name, source)
+    _SIGNATURES[name] = dict(signatures)
+    _bound.pop(name, None)
+
+
+def switches_changed() -> None:
+    """Called by every switch that changes which kernels a step launches: captured step graphs are
+    keyed by the epoch, so a step captured under the old setting is not replayed under the new one."""
+    global _switch_epoch
+    _switch_epoch += 1
+
+
+def switch_epoch() -> int:
+    return _switch_epoch
 
 
 def set_pdl(on: bool) -> None:
@@ -90,6 +114,7 @@ def set_pdl(on: bool) -> None:
     or set_pdl(False) launches plainly."""
     global _pdl
     _pdl = bool(on)
+    switches_changed()
     for handle in _bound.values():
         handle.kvad_set_pdl(int(_pdl))
 
@@ -127,6 +152,28 @@ _launches = 0
 def launch_count() -> int:
     """How many kernels of this library have been launched (or captured into a graph) so far."""
     return _launches
+
+
+def launch(handle: ctypes.CDLL, status: int) -> None:
+    """For kernels registered from outside: raises the entry point's own message on a refusal, counts the launch."""
+    _check(status, handle)
+
+
+def stream_ptr() -> c_void_p:
+    """The current CUDA stream as the entry points take it."""
+    return _stream()
+
+
+_sm_counts: dict[int, int] = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of the device (asked once per device)."""
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index or 0
+    n = _sm_counts.get(idx)
+    if n is None:
+        n = _sm_counts[idx] = int(torch.cuda.get_device_properties(idx).multi_processor_count)
+    return n
 
 
 def _check(status: int, handle: ctypes.CDLL) -> None:
@@ -169,12 +216,13 @@ class Ops:
         # (qkv at 1 row: 2.4 us against 3.9 us) and loses from 8 rows on (down-projection at 8 rows: 9.2 us
         # against 2.8 us), so it is not the default; KVAD_ROWS_LINEAR=1 or form="rows" selects it.
         self.rows_linear = dtype == torch.bfloat16 and os.environ.get("KVAD_ROWS_LINEAR", "0") == "1"
-        # One kernel for `layernorm -> linear` (at most 16 rows).  Measured on a B200 it is SLOWER than the
-        # pair under dependent launch (GPT-2 small, batch 8: 0.55 ms a step against 0.50 ms): the separate
-        # norm already hides behind the product's weight fetch, while the fused kernel puts the norm on every
-        # CTA's critical path.  So it is off unless KVAD_FUSE_NORM=1 (or this flag) turns it on.
-        self.fuse_norm = os.environ.get("KVAD_FUSE_NORM", "0") == "1"
         self._counters = None       # zeroed ints the decode kernel counts finished splits in (left zeroed by it)
+
+    def path_key(self) -> tuple:
+        """Everything on the host that decides which kernels a step of a given shape launches; part of
+        the key under which a step's CUDA graph is kept."""
+        return (_switch_epoch, self.tensor_core_linear, self.tensor_core_prefill, self.fast_decode,
+                self.rows_linear)
 
     # -- embedding -----------------------------------------------------------------
     def embed(self, tokens, positions, wte, wpe, out) -> None:
@@ -256,41 +304,6 @@ class Ops:
         _check(h.kvad_linear_simt(self.code, _ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k,
                                   epi, _stream()), h)
 
-    def ln_linear_takes(self, n_rows: int, k: int, epilogue: str) -> bool:
-        """Whether `layernorm -> linear` of these sizes runs as one kernel (few rows, bfloat16 tensor-core path,
-        a storing epilogue, and the normalised rows fitting shared memory beside the weights)."""
-        return (self.fuse_norm and self.tensor_core_linear and 1 <= n_rows <= 16 and k % 8 == 0 and k <= 2048
-                and epilogue != "residual")
-
-    def layernorm_linear(self, x, rows, n_rows: int, gain, beta, eps: float, weight, bias, out, epilogue: str = "store") -> None:
-        """out = epilogue(layernorm(x[rows]) . weight^T + bias) in one kernel; x is the float32 residual stream."""
-        _need_cuda(x, rows, gain, beta, weight, bias, out)
-        epi = EPILOGUES[epilogue]
-        if epilogue == "residual" or not (1 <= n_rows <= 16):
-            raise KernelError("layernorm_linear: takes 1..16 rows and a storing epilogue")
-        n, k = weight.shape
-        ldo = _rows_view(out, "linear output")
-        if x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1 or x.shape[1] != k:
-            raise KernelError("layernorm_linear: input must be the float32 residual stream of the weight's width")
-        if weight.dtype != torch.bfloat16 or not weight.is_contiguous():
-            raise KernelError("layernorm_linear: weight must be contiguous bfloat16")
-        want_out = torch.float32 if epi == 4 else torch.bfloat16
-        if out.dtype != want_out or tuple(out.shape) != (n_rows, n):
-            raise KernelError(f"layernorm_linear: output must be {want_out} of shape [{n_rows}, {n}]")
-        if gain.numel() != k or (beta is not None and (beta.numel() != k or beta.dtype != gain.dtype)):
-            raise KernelError("layernorm_linear: gain and bias of the norm must have the row's width and one dtype")
-        if rows is not None and (rows.dtype != torch.int32 or rows.numel() < n_rows):
-            raise KernelError("layernorm_linear: row list must be int32, one per row")
-        if rows is None and x.shape[0] < n_rows:
-            raise KernelError("layernorm_linear: fewer input rows than asked for")
-        bias_f32 = 1 if (bias is not None and bias.dtype == torch.float32) else 0
-        if bias is not None and bias.numel() != n:
-            raise KernelError(f"layernorm_linear: bias has {bias.numel()} entries for {n} outputs")
-        h = lib("linear_tcgen05")
-        _check(h.kvad_linear_tcgen05_ln(_ptr(x), x.stride(0), _ptr(rows), _ptr(gain), _ptr(beta),
-                                        1 if gain.dtype == torch.float32 else 0, float(eps), _ptr(weight), _ptr(bias),
-                                        bias_f32, _ptr(out), ldo, int(n_rows), n, k, epi, _stream()), h)
-
     # -- cache writes and attention --------------------------------------------------
     def kv_store(self, k_src, v_src, row_seq, row_pos, page_table, k_pages, v_pages) -> None:
         """Writes rows' keys and values to (sequence, position) in one layer's pages
@@ -353,10 +366,10 @@ class Ops:
         return head_dim in self.DECODE_HEAD_SIZES
 
     @staticmethod
-    def decode_splits(n_rows: int, n_heads: int, table_width: int) -> int:
+    def decode_splits(n_rows: int, n_heads: int, table_width: int, n_sms: Optional[int] = None) -> int:
         """Into how many key ranges a decode step cuts each (row, head): enough CTAs to fill the GPU
         twice over, at most one range per page.  Depends on the batch's size only, never on lengths."""
-        want = -(-2 * 148 // max(1, n_rows * n_heads))
+        want = -(-2 * (n_sms or sm_count()) // max(1, n_rows * n_heads))
         return max(1, min(want, table_width, 8))          # at most 8: the splits of a row and head form one cluster
 
     def attention_decode(self, q, out, row_seq, row_pos, page_table, k_pages, v_pages, n_heads: int, scale: float,
@@ -437,6 +450,7 @@ class Ops:
 def sample_force_general(on: bool) -> None:
     """Tests: True sends every sampling row through the selections over the whole vocabulary, also
     where a small top-k has a shorter way."""
+    switches_changed()
     h = lib("sampling")
     h.kvad_sample_force_general.argtypes = [c_int]
     h.kvad_sample_force_general.restype = None
@@ -445,6 +459,7 @@ def sample_force_general(on: bool) -> None:
 
 def prefill_force_legacy(on: bool) -> None:
     """Tests: True keeps the prompt attention of head sizes 64 and 128 on the mma.sync kernel, not the tcgen05 one."""
+    switches_changed()
     h = lib("attention_prefill")
     h.kvad_attention_prefill_force_legacy.argtypes = [c_int]
     h.kvad_attention_prefill_force_legacy.restype = None
@@ -465,6 +480,7 @@ def prefill_wait_timeouts() -> int:
 def decode_force_plain(on) -> None:
     """Tests: 1 / True keeps the decode attention of every head size on the kernel that loads through
     registers; 2 keeps the TMA-fed kernel but merges splits through global memory, not a cluster; 0: default."""
+    switches_changed()
     h = lib("attention_decode")
     h.kvad_attention_decode_force_plain.argtypes = [c_int]
     h.kvad_attention_decode_force_plain.restype = None
@@ -485,6 +501,7 @@ def decode_wait_timeouts() -> int:
 def tcgen05_load_form(mode: int) -> None:
     """Tests: 0 lets the swapped linear kernel choose between one TMA load per K block and grouped
     three-dimensional loads; 1 forces the former, 2 the latter (where K is a multiple of 64)."""
+    switches_changed()
     h = lib("linear_tcgen05")
     h.kvad_linear_tcgen05_no_3d.argtypes = [c_int]
     h.kvad_linear_tcgen05_no_3d.restype = None
@@ -493,6 +510,7 @@ def tcgen05_load_form(mode: int) -> None:
 
 def tcgen05_cluster_k(on: bool) -> None:
     """Tests: False keeps K whole under the storing epilogues of the swapped form (no reduction inside a cluster)."""
+    switches_changed()
     h = build.load("linear_tcgen05")
     h.kvad_linear_tcgen05_no_cluster_k.argtypes = [c_int]
     h.kvad_linear_tcgen05_no_cluster_k.restype = None
@@ -501,6 +519,7 @@ def tcgen05_cluster_k(on: bool) -> None:
 
 def tcgen05_plain_stores(on: bool) -> None:
     """Tests: the wide linear kernel writes its output with plain stores instead of TMA stores / reduce-adds."""
+    switches_changed()
     h = lib("linear_tcgen05")
     h.kvad_linear_tcgen05_no_tma_out.argtypes = [c_int]
     h.kvad_linear_tcgen05_no_tma_out.restype = None

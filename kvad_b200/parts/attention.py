@@ -18,6 +18,8 @@ from __future__ import annotations
 
 from typing import Optional
 
+import torch
+
 from ..cache.layout import KVNeed
 from .base import Mixer, PartSpec, build_part, register_part
 from .linear import Linear
@@ -25,8 +27,6 @@ from .linear import Linear
 
 class CausalSelfAttention(Mixer):
     graph_safe = True
-
-    accepts_deferred_norm = True       # `h` goes straight into the fused projection
 
     def __init__(self, prefix: str, width: int, n_heads: int, head_dim: int, score_scale: float,
                  n_kv_heads: Optional[int] = None, window: Optional[int] = None, bias: bool = True,
@@ -63,8 +63,31 @@ class CausalSelfAttention(Mixer):
             self.position.rotate(ctx, q, k)
         view = ctx.kv(call.cache)
         mixed = ctx.buffer((n, self.q_width))
-        ctx.attend(q, k, v, mixed, view, self.n_heads, self.score_scale, call.writes_cache)
+        self.attend(ctx, q, k, v, mixed, view, call.writes_cache)
         self.out.forward(ctx, mixed, residual, "residual")
+
+    def attend(self, ctx, q, k, v, out, view, writes_cache: bool = True) -> None:
+        """Writes the rows' keys and values to the cache entry (if this call owns it) and lets every
+        row attend over its sequence up to its own position.  The kernels are chosen by the step's
+        shape class (single-token rows or prompts) and this mixer's head size, never by lengths."""
+        ops, b, n_heads, scale = ctx.ops, ctx.batch, self.n_heads, self.score_scale
+        hd = self.head_dim
+        if b.is_decode and ops.fast_decode and ops.decode_takes(hd):
+            splits = ops.decode_splits(ctx.n_rows, n_heads, view.page_table.shape[1])
+            scratch = ctx.buffer((ctx.n_rows * n_heads * splits * (hd + 2),), torch.float32) if splits > 1 else None
+            ops.attention_decode(q, out, ctx.row_seq, ctx.row_pos, view.page_table, view.k_pages, view.v_pages,
+                                 n_heads, scale, view.window or 0, n_splits=splits, scratch=scratch,
+                                 k_new=k if writes_cache else None, v_new=v if writes_cache else None,
+                                 merge_in_kernel=True)
+            return
+        if writes_cache:
+            ops.kv_store(k, v, ctx.row_seq, ctx.row_pos, view.page_table, view.k_pages, view.v_pages)
+        if (not b.is_decode) and ops.tensor_core_prefill and ops.prefill_takes(hd):
+            ops.attention_prefill(q, out, ctx.seq_starts, ctx.kv_lens, ctx.n_seqs, b.max_new, view.page_table,
+                                  view.k_pages, view.v_pages, n_heads, scale, view.window or 0)
+        else:
+            ops.attention(q, out, ctx.row_seq, ctx.row_pos, view.page_table, view.k_pages, view.v_pages,
+                          n_heads, scale, view.window or 0)
 
 
 register_part("mixer", "causal_attention", CausalSelfAttention)

@@ -13,10 +13,7 @@ Interfaces (all rows of a step are packed; `ctx` is the step's `StepContext`):
 
 * `Norm.forward(ctx, x, rows=None) -> Tensor`: normalises rows of the
   float32 residual stream `x` (only the listed rows if `rows` is given) into
-  a new buffer of the compute dtype.  A block hands a mixer or feed-forward
-  that sets `accepts_deferred_norm = True` the result of `Norm.defer(...)`
-  instead, which may be a `DeferredNorm`: rows yet to be normalised, which a
-  `Linear` can normalise inside its own kernel.
+  a new buffer of the compute dtype.
 * `PositionEncoding.table() -> Tensor | None`: a table `[positions, width]`
   that the token embedding adds per row, or None; `rotate(ctx, q, k)`: in
   place change of a mixer's queries and keys by the rows' positions (identity
@@ -137,33 +134,6 @@ class PositionEncoding(Part):
 class Norm(Part):
     def forward(self, ctx, x: torch.Tensor, rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> torch.Tensor:
         raise NotImplementedError
-
-    def fused_params(self):
-        """(gain, bias, eps) if this is a plain LayerNorm that a following product may compute itself, else None."""
-        return None
-
-    def defer(self, ctx, x: torch.Tensor, rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None):
-        """The normalised rows, or a promise of them (`DeferredNorm`) where the consumer has said it
-        takes one (`accepts_deferred_norm`) and a following `Linear` can normalise inside its kernel."""
-        n = n_rows if n_rows is not None else (x.shape[0] if rows is None else rows.numel())
-        if self.fused_params() is not None and ctx.ops.ln_linear_takes(n, x.shape[1], "store"):
-            return DeferredNorm(ctx, self, x, rows, n)
-        return self.forward(ctx, x, rows, n)
-
-
-class DeferredNorm:
-    """Rows of the residual stream that a norm has yet to normalise.  `Linear.forward` takes it in
-    place of a tensor and fuses norm and product if it can; anyone else calls `materialize()`."""
-
-    def __init__(self, ctx, norm: Norm, x: torch.Tensor, rows, n_rows: int):
-        self.ctx, self.norm, self.x, self.rows, self.n_rows = ctx, norm, x, rows, n_rows
-        self.shape = (n_rows, x.shape[1])
-        self._done = None
-
-    def materialize(self) -> torch.Tensor:
-        if self._done is None:
-            self._done = self.norm.forward(self.ctx, self.x, self.rows, self.n_rows)
-        return self._done
 
 
 class Mixer(Part):

@@ -23,11 +23,9 @@ class PreNormBlock(Block):
         return [self.norm1, self.mixer, self.norm2, self.feed_forward]
 
     def forward(self, ctx, x, call):
-        lazy = getattr(self.mixer, "accepts_deferred_norm", False)
-        h = (self.norm1.defer if lazy else self.norm1.forward)(ctx, x, n_rows=ctx.n_rows)
+        h = self.norm1.forward(ctx, x, n_rows=ctx.n_rows)
         self.mixer.forward(ctx, h, x, call)
-        lazy = getattr(self.feed_forward, "accepts_deferred_norm", False)
-        h = (self.norm2.defer if lazy else self.norm2.forward)(ctx, x, n_rows=ctx.n_rows)
+        h = self.norm2.forward(ctx, x, n_rows=ctx.n_rows)
         self.feed_forward.forward(ctx, h, x)
 
 

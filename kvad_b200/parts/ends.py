@@ -77,7 +77,7 @@ class LMHead(Part):
         logits = ctx.buffer((n, self.vocab_size), torch.float32)
         if n == 0:
             return logits
-        h = self.norm.defer(ctx, x, rows=ctx.want_rows, n_rows=n)
+        h = self.norm.forward(ctx, x, rows=ctx.want_rows, n_rows=n)
         if self.tied:
             self.proj.weight = self.embedding.weight
         self.proj.forward(ctx, h, logits, "store_f32")

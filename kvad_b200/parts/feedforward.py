@@ -16,8 +16,6 @@ ACTIVATIONS = {"gelu_tanh": "gelu_tanh", "gelu_erf": "gelu_erf"}
 class DenseMLP(FeedForward):
     graph_safe = True
 
-    accepts_deferred_norm = True       # `h` goes straight into the up-projection
-
     def __init__(self, prefix: str, width: int, hidden: int, activation: str, bias: bool = True,
                  stored: str = "out_in", up_name: str = "up.", down_name: str = "down."):
         super().__init__(prefix)

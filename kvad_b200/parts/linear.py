@@ -13,7 +13,7 @@ from typing import Optional
 import torch
 
 from ..weights.source import TensorRequest
-from .base import DeferredNorm, Part
+from .base import Part
 
 
 class Linear(Part):
@@ -50,14 +50,6 @@ class Linear(Part):
         return [t for t in ((self.weight if self.has_weight else None), self.bias) if t is not None]
 
     def forward(self, ctx, a, out: torch.Tensor, epilogue: str = "store") -> torch.Tensor:
-        """out = epilogue(a . W^T + b).  `a` is a tensor of rows or a `DeferredNorm`: rows still to be
-        normalised, which are normalised inside the product's kernel when it has such a form."""
-        if isinstance(a, DeferredNorm):
-            params = a.norm.fused_params()
-            if params is not None and ctx.ops.ln_linear_takes(a.n_rows, self.in_features, epilogue):
-                gain, beta, eps = params
-                ctx.ops.layernorm_linear(a.x, a.rows, a.n_rows, gain, beta, eps, self.weight, self.bias, out, epilogue)
-                return out
-            a = a.materialize()
+        """out = epilogue(a . W^T + b)."""
         ctx.ops.linear(a, self.weight, self.bias, out, epilogue)
         return out

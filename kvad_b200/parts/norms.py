@@ -35,9 +35,6 @@ class LayerNorm(Norm):
     def own_tensors(self):
         return [t for t in (self.gain, self.bias) if t is not None]
 
-    def fused_params(self):
-        return (self.gain, self.bias, self.eps)
-
     def forward(self, ctx, x, rows=None, n_rows=None):
         n = n_rows if n_rows is not None else (x.shape[0] if rows is None else rows.numel())
         out = ctx.buffer((n, self.width))

@@ -19,13 +19,22 @@ TINY = {
     "C": dict(model_type="gpt2", n_layer=2, n_embd=80, n_head=6, num_key_value_heads=2, head_dim=16, n_inner=200,
               vocab_size=777, n_positions=160, layer_norm_epsilon=1e-5, activation_function="gelu_new",
               tie_word_embeddings=False),
+    # heads of 64 and 1024 positions: the tensor-core prompt attention, decode attention over up to 16 pages
+    "D": dict(model_type="gpt2", n_layer=2, n_embd=128, n_head=2, n_inner=384, vocab_size=1200, n_positions=1024,
+              layer_norm_epsilon=1e-5, activation_function="gelu_new"),
 }
-SEEDS = {"A": 11, "B": 23, "C": 37}
+SEEDS = {"A": 11, "B": 23, "C": 37, "D": 41}
+# A and B once more, in folders that this library did not write: real checkpoint layout, stored in
+# 32-bit with full mantissas (tests/plain/fixture.py); U: an untied head with a bias, stored in float16
+TINY["A32"], TINY["B32"] = TINY["A"], TINY["B"]
+TINY["U16"] = dict(TINY["A"], tie_word_embeddings=False, n_head=2)
+FOREIGN = {"A32": (13, "F32", 1), "B32": (29, "F32", 3), "U16": (31, "F16", 2)}      # seed, stored dtype, shards
 
 # How far logits may be from the plain implementation, as max |difference| / max |reference| over a
 # request.  float32 against the float64 oracle: rounding of 32-bit sums (measured 2e-7 .. 6e-7).
 # bfloat16 against the oracle that rounds activations to bfloat16 at the engine's storage points:
-# what is left is single bfloat16 roundings that fall the other way (measured up to 2.5e-3).
+# what is left is single bfloat16 roundings that fall the other way (measured up to 2.5e-3).  That
+# oracle follows the engine's storage decisions, so only the float32 runs are an independent statement.
 TOL = {"float32": 5e-6, "bfloat16": 8e-3}
 
 
@@ -46,10 +55,16 @@ def model_dirs(tmp_path_factory):
     """name -> folder with config.json + model.safetensors (bfloat16 storage), made once per session."""
     from kvad_b200 import write_random_model
 
+    from tests.plain.fixture import write_gpt2_folder
+
     out = {}
     for name, cfg in TINY.items():
         d = tmp_path_factory.mktemp(f"tiny{name}")
-        write_random_model(str(d), cfg, SEEDS[name])
+        if name in FOREIGN:
+            seed, stored, shards = FOREIGN[name]
+            write_gpt2_folder(str(d), cfg, seed, stored, shards)
+        else:
+            write_random_model(str(d), cfg, SEEDS[name])
         out[name] = str(d)
     return out
 

@@ -7,7 +7,10 @@ and not on a run of the reference.  It shares no code with `kvad_b200`: it
 reads safetensors with its own few lines, takes config.json's keys itself and
 computes with NumPy in float64 (the oracle) - or, with `round_to="bfloat16"`,
 rounds activations to bfloat16 at the places where a bfloat16 engine stores
-them, so that a bfloat16 run can be compared tightly.
+them, and matrices to bfloat16 as a bfloat16 engine holds them, so that a
+bfloat16 run can be compared tightly.  That second mode follows the engine's
+storage decisions (which activations and which tensors are held in bfloat16);
+only the float64 mode is a statement independent of the engine.
 """
 from __future__ import annotations
 
@@ -20,13 +23,30 @@ import numpy as np
 
 
 # ----------------------------------------------------------------------------- files
-def read_safetensors(path):
+def read_model_files(model_dir):
+    """`model.safetensors`, or the shards that `model.safetensors.index.json` names in its
+    `weight_map` (crates/llm/src/weights.rs:231-239, 269-282).  Returns (tensors, stored dtypes)."""
+    single = os.path.join(model_dir, "model.safetensors")
+    if os.path.isfile(single):
+        files = [single]
+    else:
+        with open(os.path.join(model_dir, "model.safetensors.index.json")) as f:
+            files = sorted({os.path.join(model_dir, fn) for fn in json.load(f)["weight_map"].values()})
+    tensors, dtypes = {}, {}
+    for fn in files:
+        t, d = read_safetensors(fn, with_dtypes=True)
+        tensors.update(t)
+        dtypes.update(d)
+    return tensors, dtypes
+
+
+def read_safetensors(path, with_dtypes=False):
     """u64 header length, JSON header, blob (crates/llm/src/weights.rs:9-13)."""
     with open(path, "rb") as f:
         (n,) = struct.unpack("<Q", f.read(8))
         header = json.loads(f.read(n))
         blob = f.read()
-    out = {}
+    out, dtypes = {}, {}
     for name, info in header.items():
         if name == "__metadata__":
             continue
@@ -44,7 +64,8 @@ def read_safetensors(path):
         else:
             raise ValueError(f"plain reader: dtype {dt}")
         out[name] = a.reshape(info["shape"])
-    return out
+        dtypes[name] = dt
+    return (out, dtypes) if with_dtypes else out
 
 
 def round_bf16(a):
@@ -60,13 +81,17 @@ class PlainGpt2:
         with open(os.path.join(model_dir, "config.json")) as f:
             c = json.load(f)
         self.c = c
-        w = read_safetensors(os.path.join(model_dir, "model.safetensors"))
+        w, stored = read_model_files(model_dir)
         # names may carry a prefix (crates/llm/src/weights.rs:866-868)
         self.w = {}
         for k, v in w.items():
+            dt = stored[k]
             for p in ("transformer.", "model."):
                 if k.startswith(p):
                     k = k[len(p):]
+            # a bfloat16 engine holds everything in bfloat16 except vectors that the file stores in 32-bit
+            if round_to == "bfloat16" and v.dtype.kind == "f" and not (dt == "F32" and v.ndim <= 1):
+                v = round_bf16(v)
             self.w[k] = v
         # keys and defaults: crates/llm/src/model/mod.rs:343-364
         self.E = c.get("n_embd", c.get("hidden_size"))
@@ -169,12 +194,13 @@ class PlainGpt2:
         return out
 
     # ------------------------------------------------------------------------- whole
-    def logits(self, tokens, order=None):
-        """Logits at every position of one whole sequence, float64 [len, vocab]."""
+    def logits(self, tokens, order=None, rows=None):
+        """Logits at every position of one whole sequence, float64 [len, vocab]; with `rows`, only at
+        those positions (the whole sequence still runs through the blocks)."""
         x = self.embed(tokens)
         for i in (range(self.L) if order is None else order):
             x = self.block(x, i)
-        return self.head(x)
+        return self.head(x if rows is None else x[np.asarray(rows)])
 
     def greedy(self, prompt, n, stop=()):
         """Greedy continuation, recomputing the whole sequence for each token."""

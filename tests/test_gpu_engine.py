@@ -9,7 +9,9 @@ from kvad_b200 import StepEntry
 from tests.conftest import TINY, TOL, random_tokens, rel_err
 
 pytestmark = pytest.mark.gpu
-CASES = [(c, d) for c in ("A", "B", "C") for d in ("float32", "bfloat16")]
+CASES = [(c, d) for c in ("A", "B", "C", "D") for d in ("float32", "bfloat16")]
+# folders in real checkpoint layout that the library did not write, stored in 32-bit / float16, sharded
+CASES += [("A32", "float32"), ("B32", "float32"), ("B32", "bfloat16"), ("U16", "float32"), ("U16", "bfloat16")]
 
 
 def poison(engine):
@@ -120,6 +122,33 @@ def test_long_decoding(engines, plains, name, dtype):
     e.cache.book.check_all_free()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_prompts_in_two_portions_then_decoding_across_page_edges(engines, plains, dtype):
+    """Heads of 64, 1024 positions: two prompts given in two portions each (the second continues cached
+    positions and crosses a 128-row tile and a page edge), then single tokens across positions 512 and 704."""
+    e, plain, cfg = engines("D", dtype, max_tokens=2048), plains("D", dtype), TINY["D"]
+    poison(e)
+    V = cfg["vocab_size"]
+    a, b = random_tokens(450, 716, V), random_tokens(451, 531, V)
+    ra, rb = plain.logits(a), plain.logits(b)
+    sa, sb = e.open(), e.open()
+    got = e.step([StepEntry(sa, a[:333], range(333)), StepEntry(sb, b[:300], range(300))]).cpu().numpy()
+    assert rel_err(got[:333], ra[:333]) < TOL[dtype] and rel_err(got[333:], rb[:300]) < TOL[dtype]
+    got = e.step([StepEntry(sa, a[333:700], range(367)), StepEntry(sb, b[300:505], range(205))]).cpu().numpy()
+    assert rel_err(got[:367], ra[333:700]) < TOL[dtype], "second portion of a"
+    assert rel_err(got[367:], rb[300:505]) < TOL[dtype], "second portion of b"
+    for j in range(16):
+        got = e.step([StepEntry(sa, [a[700 + j]], [0]), StepEntry(sb, [b[505 + j]], [0])]).cpu().numpy()
+        assert rel_err(got[0], ra[700 + j]) < TOL[dtype], f"a at {700 + j}"
+        assert rel_err(got[1], rb[505 + j]) < TOL[dtype], f"b at {505 + j}"
+    e.close(sa)
+    for j in range(16, 26):                                  # b alone, past the page edge at 512
+        got = e.step([StepEntry(sb, [b[505 + j]], [0])]).cpu().numpy()
+        assert rel_err(got[0], rb[505 + j]) < TOL[dtype], f"b at {505 + j}"
+    e.close(sb)
+    e.cache.book.check_all_free()
+
+
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_first_tokens_of_a_sequence(engines, plains, name, dtype):
     e, plain, cfg = engines(name, dtype), plains(name, dtype), TINY[name]
@@ -162,7 +191,10 @@ def test_greedy_generation_through_the_entry_point(engines, plains, model_dirs, 
     tolerance) the oracle's best continuation of the engine's own prefix."""
     from tests.plain.gpt2_plain import PlainGpt2
     e, cfg = engines(name, dtype), TINY[name]
-    oracle = PlainGpt2(model_dirs[name])
+    from tests.conftest import FOREIGN
+    # the float64 oracle on the stored values; where a bfloat16 engine holds other values than the file
+    # stores (a 32-bit or float16 file), the oracle that rounds as the engine does
+    oracle = plains(name, dtype) if (name in FOREIGN and dtype == "bfloat16") else PlainGpt2(model_dirs[name])
     prompts = [random_tokens(700 + i, n, cfg["vocab_size"]) for i, n in enumerate([5, 11, 17])]
     outs = e.generate(prompts, max_tokens=8, temperature=0.0)
     e.cache.book.check_all_free()
@@ -179,6 +211,28 @@ def test_greedy_generation_through_the_entry_point(engines, plains, model_dirs, 
     # batches one after another give the same tokens as all at once
     again = e.generate(prompts, max_tokens=8, temperature=0.0, batch_size=2)
     assert again == outs
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16"), ("D", "bfloat16")])
+def test_decode_run_gives_the_tokens_of_generate(engines, plains, model_dirs, name, dtype):
+    """`Engine.decode_run` (decoding with the chosen tokens fed back on the device, the road the benchmark
+    times) chooses the same tokens as `Engine.generate`, and in 32-bit they are the oracle's greedy tokens."""
+    e, cfg = engines(name, dtype), TINY[name]
+    prompts = [random_tokens(720 + i, n, cfg["vocab_size"]) for i, n in enumerate([9, 4, 15, 6, 1])]
+    want = e.generate(prompts, max_tokens=12, temperature=0.0, stop_token_ids=[])
+    slots = [e.open() for _ in prompts]
+    logits = e.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+    first = logits.argmax(-1).tolist()
+    hist = e.decode_run(slots, first, 11).cpu().numpy()
+    for s in slots:
+        e.close(s)
+    e.cache.book.check_all_free()
+    got = [[first[i]] + hist[:, i].tolist() for i in range(len(prompts))]
+    assert got == want
+    if dtype == "float32":
+        oracle = plains(name, dtype)
+        for p, o in zip(prompts, got):
+            assert o == oracle.greedy(p, 12), len(p)
 
 
 def test_stop_token_and_unequal_ends(engines, plains):
@@ -224,9 +278,10 @@ def test_dependent_launch_changes_no_result(engines, plains):
     outs = {}
     try:
         for on in (True, False):
-            ops.set_pdl(on)
+            ops.set_pdl(on)                         # a new switch epoch: no graph captured under the other setting is replayed
             for dtype in ("float32", "bfloat16"):
                 e = engines("A", dtype)
+                assert not any(k[-1] == e.ops.path_key() for k in e._graphs), "a graph of the other arm would be replayed"
                 s = e.open()
                 got = [e.step([StepEntry(s, t[:90], range(90))]).cpu().numpy()]
                 for j in range(90, 100):
@@ -238,24 +293,6 @@ def test_dependent_launch_changes_no_result(engines, plains):
     assert np.array_equal(outs[(True, "float32")], outs[(False, "float32")])
     ref = plains("A", "bfloat16").logits(t)
     assert rel_err(outs[(True, "bfloat16")], ref) < TOL["bfloat16"] and rel_err(outs[(False, "bfloat16")], ref) < TOL["bfloat16"]
-
-
-def test_norm_fused_into_the_product_changes_no_result(engines, plains):
-    """Decoding with `layernorm -> linear` as one kernel (an option, off by default) gives the same logits."""
-    e, plain = engines("B", "bfloat16"), plains("B", "bfloat16")
-    t = random_tokens(960, 40, 1000)
-    ref = plain.logits(t)
-    try:
-        for fused in (True, False):
-            e.ops.fuse_norm = fused
-            s = e.open()
-            e.step([StepEntry(s, t[:30], [])])
-            for j in range(30, 40):
-                got = e.step([StepEntry(s, [t[j]], [0])]).cpu().numpy()
-                assert rel_err(got[0], ref[j]) < TOL["bfloat16"], (fused, j)
-            e.close(s)
-    finally:
-        e.ops.fuse_norm = False
 
 
 def test_repeated_step_shapes_replay_a_graph_with_the_same_result(engines, plains):
@@ -296,3 +333,23 @@ def test_random_weights_entry_point(tmp_path):
     assert again.generate([prompt], max_tokens=6, temperature=0.0, stop_token_ids=[])[0] == got
     other = Engine.random(TINY["B"], seed=6, dtype="float32", max_tokens=1024)
     assert other.generate([prompt], max_tokens=6, temperature=0.0, stop_token_ids=[])[0] != got
+
+
+def test_random_weights_stored_in_32_bit(tmp_path):
+    """The random-weights mode storing float32: the 32-bit engine multiplies by values bfloat16 cannot hold."""
+    from kvad_b200 import Engine, write_random_model
+    from tests.plain.gpt2_plain import PlainGpt2, round_bf16
+    d = str(tmp_path / "m32")
+    write_random_model(d, TINY["B"], 9, store_dtype="float32")
+    plain = PlainGpt2(d)
+    w = plain.w["h.0.mlp.c_fc.weight"]
+    assert np.mean(round_bf16(w) != w) > 0.9
+    e = Engine.from_pretrained(d, "float32", max_tokens=512)
+    t = random_tokens(12, 80, TINY["B"]["vocab_size"])
+    ref = plain.logits(t)
+    s = e.open()
+    got = [e.step([StepEntry(s, t[:70], range(70))]).cpu().numpy()]
+    for j in range(70, 80):
+        got.append(e.step([StepEntry(s, [t[j]], [0])]).cpu().numpy())
+    e.close(s)
+    assert rel_err(np.concatenate(got), ref) < TOL["float32"]

@@ -111,8 +111,7 @@ def test_linear_cuda_cores(dtype):
     # odd shapes of bisand/kvad's own GEMM test (crates/llm/src/tensor.rs:487-500) and larger ones
     for m, n, k in [(9, 13, 7), (8, 16, 4), (5, 32, 1), (6, 8, 9), (1, 1031, 200), (130, 70, 333), (64, 64, 16)]:
         for epi in ("store", "gelu_tanh", "gelu_erf", "residual", "store_f32"):
-            tol = KTOL[dtype] if epi in ("residual", "store_f32") or dtype == "float32" else KTOL[dtype]
-            assert linear_case(ops, dtype, m, n, k, epi, g) < tol, (m, n, k, epi)
+            assert linear_case(ops, dtype, m, n, k, epi, g) < KTOL[dtype], (m, n, k, epi)
     assert linear_case(ops, dtype, 7, 19, 24, "store", g, bias=False, strided=True) < KTOL[dtype]
     assert linear_case(ops, dtype, 7, 19, 24, "store_f32", g, bias_f32=True) < KTOL[dtype]
 
@@ -558,48 +557,6 @@ def test_attention_prefill_finds_one_far_key():
                           1, n, dev(table), dev(kp), dev(vp), 1, 1.0, 0)
     assert (out.float().cpu()[n - 1] - torch.arange(hd)).abs().max() < 0.05 * hd
     assert not ops.prefill_takes(256) and not ops.prefill_takes(24)
-
-
-@pytest.mark.parametrize("m", [1, 3, 8, 13, 16])
-def test_layernorm_fused_into_the_product(m):
-    """out = epi(LayerNorm(x[rows]) . W^T + b) in one kernel, against the float64 reference that rounds the
-    normalised rows to bfloat16 where the unfused pair stores them."""
-    from kvad_b200.ops import tcgen05_wait_timeouts
-    from tests.plain.gpt2_plain import round_bf16
-    ops = Ops(torch.bfloat16)
-    ops.fuse_norm = True
-    g = torch.Generator().manual_seed(300 + m)
-    for n, k in [(2304, 768), (1000, 96), (50, 320), (333, 64), (50257, 768), (777, 1600)]:
-        for epi in ("store", "gelu_tanh", "gelu_erf", "store_f32"):
-            for params in ("bf16", "f32"):
-                assert ops.ln_linear_takes(m, k, epi)
-                x = torch.randn(m + 5, k, generator=g) * 2 + 0.3
-                rows = torch.randperm(m + 5, generator=g)[:m].to(torch.int32)
-                gain, beta = 1 + 0.2 * torch.randn(k, generator=g), 0.2 * torch.randn(k, generator=g)
-                if params == "bf16":
-                    gain, beta = gain.bfloat16(), beta.bfloat16()
-                w = (torch.randn(n, k, generator=g) / math.sqrt(k)).bfloat16()
-                b = torch.randn(n, generator=g).bfloat16()
-                xd = x.double()[rows.long()]
-                mean, var = xd.mean(-1, keepdim=True), xd.var(-1, unbiased=False, keepdim=True)
-                h = torch.from_numpy(round_bf16(((xd - mean) / torch.sqrt(var + 1e-5) * gain.double() + beta.double()).numpy()))
-                ref = h @ w.double().t() + b.double()
-                ref = gelu_tanh(ref) if epi == "gelu_tanh" else (gelu_erf(ref) if epi == "gelu_erf" else ref)
-                out = torch.full((m, n), float("nan"), device="cuda", dtype=torch.float32 if epi == "store_f32" else torch.bfloat16)
-                ops.layernorm_linear(dev(x), dev(rows), m, dev(gain), dev(beta), 1e-5, dev(w), dev(b), out, epi)
-                assert rel(out, ref) < KTOL["bfloat16"], (m, n, k, epi, params)
-    # without a row list and without a norm bias
-    x = torch.randn(m, 128, generator=g)
-    gain = torch.randn(128, generator=g).bfloat16()
-    w = (torch.randn(40, 128, generator=g) * 0.1).bfloat16()
-    xd = x.double()
-    h = torch.from_numpy(round_bf16(((xd - xd.mean(-1, keepdim=True)) / torch.sqrt(xd.var(-1, unbiased=False, keepdim=True) + 1e-3) * gain.double()).numpy()))
-    out = torch.full((m, 40), float("nan"), device="cuda", dtype=torch.bfloat16)
-    ops.layernorm_linear(dev(x), None, m, dev(gain), None, 1e-3, dev(w), None, out, "store")
-    assert rel(out, h @ w.double().t()) < KTOL["bfloat16"]
-    assert not ops.ln_linear_takes(17, 768, "store") and not ops.ln_linear_takes(8, 768, "residual")
-    assert not ops.ln_linear_takes(8, 2056, "store")
-    assert tcgen05_wait_timeouts() == 0
 
 
 @pytest.mark.parametrize("m", [1, 2, 3, 4, 7, 8, 13, 16])

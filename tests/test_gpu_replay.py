@@ -30,7 +30,8 @@ def read(out_dir, step, vocab):
     return np.fromfile(os.path.join(out_dir, f"{step}.f32"), dtype="<f4").reshape(-1, vocab)
 
 
-@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("B", "bfloat16")])
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("B", "bfloat16"),
+                                        ("B32", "float32"), ("D", "bfloat16")])
 def test_three_ways_of_cutting(model_dirs, plains, tmp_path, name, dtype):
     cfg, plain = TINY[name], plains(name, dtype)
     V, P = cfg["vocab_size"], cfg["n_positions"]

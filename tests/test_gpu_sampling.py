@@ -145,3 +145,68 @@ def test_command_line_runs_and_matches_the_entry_point(model_dirs, engines):
     # a request's tokens do not depend on its company in the batch
     both = e.generate([prompt, random_tokens(78, 9, 512)], max_tokens=12, temperature=0.8, top_k=40, top_p=0.95, seed=3)
     assert both[0] == a[0]
+
+
+def test_command_line_takes_a_text_prompt_through_tokenizer_json(model_dirs, engines, tmp_path):
+    """`kvad run --prompt TEXT`: the folder's tokenizer.json turns the text into ids and the ids back into
+    text; a base model's output starts with its prompt (crates/kvad/src/main.rs:1583-1599)."""
+    tokenizers = pytest.importorskip("tokenizers")
+    import shutil
+    d = str(tmp_path / "with_tokenizer")
+    shutil.copytree(model_dirs["A"], d)
+    vocab = {f"w{i}": i for i in range(512)}
+    tok = tokenizers.Tokenizer(tokenizers.models.WordLevel(vocab, unk_token="w0"))
+    tok.pre_tokenizer = tokenizers.pre_tokenizers.Whitespace()
+    tok.save(os.path.join(d, "tokenizer.json"))
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "kvad"), "run", "--model", d, "--prompt", "w5 w17 w3 w250",
+                           "--max-tokens", "6", "--greedy", "--dtype", "f32"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-1500:]
+    want = engines("A", "float32").generate([[5, 17, 3, 250]], max_tokens=6, temperature=0.0)[0]
+    assert proc.stdout.split() == ["w5", "w17", "w3", "w250"] + [f"w{t}" for t in want]
+    # without a tokenizer a text prompt is refused with a hint, not guessed at
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "kvad"), "run", "--model", model_dirs["A"], "--prompt", "w5",
+                           "--max-tokens", "2"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 2 and "--tokens" in proc.stderr
+
+
+class _BusyBackend:
+    """The engine as the generation loop's backend, with the stream kept busy before every launch so that
+    queued host-to-device copies lag far behind the host."""
+
+    def __init__(self, engine, pipelined):
+        self.e = engine
+        self.ballast = torch.empty(1 << 30, dtype=torch.uint8, device=engine.device)
+        self.open, self.close, self.room = engine.open, engine.close, engine.room
+        if pipelined:
+            self.launch_step = self._launch_step
+
+    def _busy(self):
+        for _ in range(3):
+            self.ballast.zero_()
+
+    def step_and_sample(self, entries, samplers):
+        self._busy()
+        return self.e.step_and_sample(entries, samplers)
+
+    def _launch_step(self, entries, samplers, device_fed=False):
+        self._busy()
+        return self.e.launch_step(entries, samplers, device_fed)
+
+
+def test_sampled_generation_a_step_ahead_draws_the_same_tokens(engines):
+    """The loop launches a step ahead of the one it waits for; each step's sampling options and uniform
+    numbers go up through a ring of staging buffers.  With the device lagging the host by several steps'
+    worth of work, the tokens are those of the loop that waits for every step."""
+    from kvad_b200.engine.generate import Request, run_all
+    from kvad_b200.sampling import SamplingParams
+    e = engines("A", "float32")
+    prompts = [random_tokens(90 + i, n, 512) for i, n in enumerate([6, 3, 11, 8])]
+
+    def run(pipelined):
+        reqs = [Request(list(p), 40, SamplingParams(0.9, 50, 0.95, 100 + i), frozenset()) for i, p in enumerate(prompts)]
+        run_all(_BusyBackend(e, pipelined), reqs, 4)
+        return [r.generated for r in reqs]
+
+    ahead, plain_loop = run(True), run(False)
+    assert ahead == plain_loop and all(len(o) == 40 for o in ahead)
+    e.cache.book.check_all_free()

@@ -6,7 +6,9 @@
    batches, a reused slot - without a change to any file of the package.
 2. A run order that names a block twice and lets a call read the keys and values another call wrote.
 
-The toy parts compute with torch operators: they are test fixtures, not kernels of the library.
+The toy parts compute with torch operators: they are test fixtures, not kernels of the library -
+except the toy rotary encoding, which brings a CUDA kernel of its own (tests/kernels/toy_rotary.cu)
+through `ops.register_kernels`, the door a real part with its own kernel would use.
 """
 import json
 import math
@@ -303,29 +305,33 @@ def test_a_position_encoding_that_acts_inside_the_mixer(model_dirs, plains):
         inv = THETA ** (-np.arange(0, HD, 2) / HD)
         return np.asarray(positions, dtype=np.float64)[:, None] * inv[None, :]
 
+    from ctypes import c_double, c_int, c_int64, c_void_p
+    from kvad_b200 import ops as kops
+    kops.register_kernels("toy_rotary", os.path.join(os.path.dirname(__file__), "kernels", "toy_rotary.cu"),
+                          {"toy_rotary": [c_int, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_double, c_void_p]})
+
     class Rotary(PositionEncoding):
+        graph_safe = True              # its kernel reads the rows' positions from device memory
+
         def __init__(self, prefix, head_dim):
             super().__init__(prefix)
             self.head_dim = head_dim
 
         def rotate(self, ctx, q, k):
-            pos = ctx.row_pos[:ctx.n_rows].double()
-            inv = torch.tensor(THETA ** (-np.arange(0, self.head_dim, 2) / self.head_dim), device=q.device)
-            ang = pos[:, None] * inv[None, :]
-            cos, sin = torch.cos(ang), torch.sin(ang)
+            h = kops.lib("toy_rotary")
             for t in (q, k):
-                v = t.double().view(t.shape[0], -1, self.head_dim // 2, 2)
-                a, b = v[..., 0].clone(), v[..., 1].clone()
-                v[..., 0] = a * cos[:, None, :] - b * sin[:, None, :]
-                v[..., 1] = a * sin[:, None, :] + b * cos[:, None, :]
-                t.copy_(v.view(t.shape[0], -1).to(t.dtype))
+                assert t.stride(1) == 1 and t.shape[1] % self.head_dim == 0
+                kops.launch(h, h.toy_rotary(ctx.ops.code, c_void_p(t.data_ptr()), t.stride(0), c_void_p(ctx.row_pos.data_ptr()),
+                                            ctx.n_rows, t.shape[1] // self.head_dim, self.head_dim, THETA, kops.stream_ptr()))
 
     def plan(cfg):
         base = gpt2.plan(cfg)
         blocks = [PartSpec(b.kind, {**b.params, "mixer": b.params["mixer"].with_params(position=PartSpec("toy_rotary", {"head_dim": HD}))})
                   for b in base.blocks]
         emb = PartSpec("token_embedding", {**base.embedding.params, "position": PartSpec("none", {})})
-        return ModelPlan(**{**base.__dict__, "arch_id": "gpt2_rotary", "blocks": tuple(blocks), "embedding": emb})
+        # no position table bounds this model; the plan states the range the encoding is meant for
+        return ModelPlan(**{**base.__dict__, "arch_id": "gpt2_rotary", "blocks": tuple(blocks), "embedding": emb,
+                            "max_positions": 300})
 
     register_part("position", "toy_rotary", Rotary)
     register(Architecture("gpt2_rotary", ("gpt2_rotary",), "gpt2 parts, toy rotary positions", gpt2.read_config, plan))
@@ -340,7 +346,8 @@ def test_a_position_encoding_that_acts_inside_the_mixer(model_dirs, plains):
             ck.close()
             write_safetensors(os.path.join(d, "model.safetensors"), tensors)
             e = Engine.from_pretrained(d, "float32", max_tokens=512)
-        assert e.max_positions is None and not e.use_graphs
+        assert e.max_positions == 300 and e.room(100) == 200 and e.cache.table_width == 5
+        assert e.use_graphs                     # every part, the toy one included, launches by shape only
         plain = plains("A")
 
         def reference(tokens):
@@ -363,12 +370,17 @@ def test_a_position_encoding_that_acts_inside_the_mixer(model_dirs, plains):
 
         t = random_tokens(41, 150, 512)                    # beyond the 128 positions the learned table had
         ref = reference(t)
+        before = kops.launch_count()
         s = e.open()
         got = [e.step([StepEntry(s, t[:140], range(140))]).cpu().numpy()]
-        for j in range(140, 150):
+        for j in range(140, 150):                          # the third and later single-token steps replay a captured graph
             got.append(e.step([StepEntry(s, [t[j]], [0])]).cpu().numpy())
-        e.close(s)
         assert rel_err(np.concatenate(got), ref) < 1e-5
+        assert kops.launch_count() > before and any("toy_rotary" in p for p in __import__("kvad_b200.csrc.build", fromlist=["x"]).loaded_paths())
+        with pytest.raises(Exception, match="context window of 300"):
+            e.step([StepEntry(s, random_tokens(42, 151, 512), [0])])
+        e.close(s)
+        e.cache.book.check_all_free()
     finally:
         unregister("gpt2_rotary")
         unregister_part("position", "toy_rotary")

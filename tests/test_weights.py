@@ -150,3 +150,37 @@ def test_random_mode_is_seeded(tmp_path):
 
 def test_collapse():
     assert collapse(["h.0.x", "h.1.x", "ln_f.weight"]) == ["h.*.x (2 tensors)", "ln_f.weight"]
+
+
+@pytest.mark.parametrize("name", ["A32", "B32", "U16"])
+def test_folders_the_library_did_not_write(model_dirs, name):
+    """Real checkpoint layout from tests/plain/fixture.py: `transformer.` names, Conv1D matrices stored
+    [in, out], stored mask buffers, 32-bit or float16 storage, one file or shards behind an index.
+    The loader's tensors equal what the plain reader makes of the same files."""
+    from tests.conftest import FOREIGN
+    from tests.plain.gpt2_plain import read_model_files
+    d = model_dirs[name]
+    _, stored, shards = FOREIGN[name]
+    assert os.path.isfile(os.path.join(d, "model.safetensors")) == (shards == 1)
+    assert os.path.isfile(os.path.join(d, "model.safetensors.index.json")) == (shards > 1)
+    m = load(d)
+    raw, dtypes = read_model_files(d)
+    assert set(dtypes.values()) <= {"I64", {"F32": "F32", "F16": "F16"}[stored]}
+    blk = m.blocks[1]
+    for got, key, transposed in [(blk.mixer.qkv.weight, "attn.c_attn.weight", True), (blk.mixer.out.weight, "attn.c_proj.weight", True),
+                                 (blk.feed_forward.up.weight, "mlp.c_fc.weight", True), (blk.feed_forward.down.bias, "mlp.c_proj.bias", False),
+                                 (blk.norm2.gain, "ln_2.weight", False)]:
+        want = raw["transformer.h.1." + key]
+        assert got.dtype == torch.float32
+        assert np.array_equal(got.double().numpy(), want.T if transposed else want), key
+    assert np.array_equal(m.embedding.weight.double().numpy(), raw["transformer.wte.weight"])      # never transposed
+    if name == "U16":
+        assert not m.head.tied and np.array_equal(m.head.proj.weight.double().numpy(), raw["lm_head.weight"])
+        assert np.array_equal(m.head.proj.bias.double().numpy(), raw["lm_head.bias"])
+    if stored == "F32":                     # values that bfloat16 cannot hold: a path that rounded them would show
+        w = raw["transformer.h.0.attn.c_attn.weight"]
+        from tests.plain.gpt2_plain import round_bf16
+        assert np.mean(round_bf16(w) != w) > 0.95
+        bf = load(d, torch.bfloat16)
+        assert bf.blocks[0].mixer.qkv.weight.dtype == torch.bfloat16 and bf.blocks[0].norm1.gain.dtype == torch.float32
+        assert np.array_equal(bf.blocks[0].mixer.qkv.weight.double().numpy(), round_bf16(w).T)

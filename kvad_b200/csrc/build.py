@@ -27,6 +27,7 @@ from concurrent.futures import ThreadPoolExecutor
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
           "-shared", "-Xcompiler", "-fPIC"]
+_FLAGS += os.environ.get("KVAD_NVCC_FLAGS", "").split()      # more flags for every library (part of a build's name)
 #: every kernel library of the package, in the order `build_all` compiles them
 LIBRARIES = ("rows", "linear_simt", "attention_simt", "sampling", "linear_tcgen05", "linear_rows",
              "attention_prefill", "attention_decode")
@@ -156,7 +157,7 @@ def compile_library(name: str, *, verbose: bool = True) -> str:
             pass
         raise BuildError(f"nvcc failed on {name}.cu (exit {proc.returncode}):\n{out}")
     os.replace(tmp, target)
-    for old in os.listdir(os.path.dirname(target)):          # builds of earlier versions of this source
+    for old in ([] if os.environ.get("KVAD_NVCC_FLAGS") else os.listdir(os.path.dirname(target))):   # builds of earlier versions of this source
         if old.startswith(f"libkvad_{name}.") and old.endswith(".so") and old != os.path.basename(target):
             try:
                 os.remove(os.path.join(os.path.dirname(target), old))

@@ -141,7 +141,7 @@ def libraries_for(dtype: torch.dtype) -> list[str]:
     names = ["rows", "linear_simt", "attention_simt", "sampling"]
     if dtype == torch.bfloat16:
         names += [n for n in ("linear_tcgen05", "attention_prefill", "attention_decode") if n in build.sources()]
-        if os.environ.get("KVAD_ROWS_LINEAR", "0") == "1":
+        if "linear_rows" in build.sources():
             names.append("linear_rows")
     return names
 
@@ -212,17 +212,19 @@ class Ops:
         self.tensor_core_prefill = dtype == torch.bfloat16 and "attention_prefill" in build.sources()
         self.fast_decode = dtype == torch.bfloat16 and "attention_decode" in build.sources()
         # Up to 16 rows the product can also run as a stream of weights through registers on the CUDA cores
-        # (linear_rows.cu).  Measured on a B200 it beats the tensor-core kernel only at one or two rows
-        # (qkv at 1 row: 2.4 us against 3.9 us) and loses from 8 rows on (down-projection at 8 rows: 9.2 us
-        # against 2.8 us), so it is not the default; KVAD_ROWS_LINEAR=1 or form="rows" selects it.
-        self.rows_linear = dtype == torch.bfloat16 and os.environ.get("KVAD_ROWS_LINEAR", "0") == "1"
+        # (linear_rows.cu).  Measured on a B200 it beats the tensor-core kernel at one or two rows (qkv at 1 row:
+        # 2.4 us against 3.9 us; a GPT-2 small decode step at batch 1: 0.286 ms against 0.326 ms, at batch 2: 0.314
+        # against 0.319) and loses from 4 rows on (batch 4: 0.410 ms against 0.327), and it loses on the output head
+        # (50257 outputs: the step is 0.307 ms with it, 0.286 without).  So it takes products of at most
+        # `rows_linear_max` rows and `ROWS_LINEAR_MAX_OUT` outputs; form="rows" selects it for any count up to 16.
+        self.rows_linear_max = 2 if dtype == torch.bfloat16 and "linear_rows" in build.sources() else 0
         self._counters = None       # zeroed ints the decode kernel counts finished splits in (left zeroed by it)
 
     def path_key(self) -> tuple:
         """Everything on the host that decides which kernels a step of a given shape launches; part of
         the key under which a step's CUDA graph is kept."""
         return (_switch_epoch, self.tensor_core_linear, self.tensor_core_prefill, self.fast_decode,
-                self.rows_linear)
+                self.rows_linear_max)
 
     # -- embedding -----------------------------------------------------------------
     def embed(self, tokens, positions, wte, wpe, out) -> None:
@@ -260,6 +262,8 @@ class Ops:
                                 float(eps), _stream()), h)
 
     # -- linear --------------------------------------------------------------------
+    ROWS_LINEAR_MAX_OUT = 8192
+
     def linear(self, a, weight, bias, out, epilogue: str = "store", *, tile: int = 0, splits: int = 0,
                form: str = "auto") -> None:
         """out = epilogue(a . weight^T + bias); weight is [out_features, in_features].
@@ -286,7 +290,7 @@ class Ops:
             bias_f32 = 1 if bias.dtype == torch.float32 else 0
             if not bias_f32 and bias.dtype != torch.bfloat16:
                 raise KernelError(f"linear: bias must be float32 or bfloat16, not {bias.dtype}")
-        if (self.dtype == torch.bfloat16 and (form == "rows" or (self.rows_linear and form == "auto")) and m <= 16 and k <= 4096 and k % 8 == 0 and lda % 8 == 0
+        if (self.dtype == torch.bfloat16 and (form == "rows" or (form == "auto" and m <= self.rows_linear_max and n <= self.ROWS_LINEAR_MAX_OUT)) and m <= 16 and k <= 4096 and k % 8 == 0 and lda % 8 == 0
                 and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
             h = lib("linear_rows")
             _check(h.kvad_linear_rows(_ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k, epi,

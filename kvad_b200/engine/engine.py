@@ -149,7 +149,9 @@ class Engine:
         self._sample_bufs = None
         self.eos_token_ids = tuple(model.plan.eos_token_ids)
         self.verbose = verbose
-        self.use_graphs = model.graph_safe     # a part that reads host-side step data keeps the model on plain launches
+        from .. import profile
+        # a part that reads host-side step data keeps the model on plain launches; so does the per-operation time table
+        self.use_graphs = model.graph_safe and not profile.enabled()
         self.max_graphs = 48            # captured step shapes kept (least recently used go first)
         self._graphs: "collections.OrderedDict" = collections.OrderedDict()
         self._decode_plans: dict = {}

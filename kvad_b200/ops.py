@@ -55,7 +55,7 @@ _SIGNATURES = {
         "kvad_linear_tcgen05_status": [],
     },
     "linear_rows": {
-        "kvad_linear_rows": [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int,
+        "kvad_linear_rows": [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int,
                              c_void_p],
     },
     "attention_simt": {
@@ -139,10 +139,9 @@ def lib(name: str) -> ctypes.CDLL:
 def libraries_for(dtype: torch.dtype) -> list[str]:
     """Which kernel libraries a model of this compute dtype loads."""
     names = ["rows", "linear_simt", "attention_simt", "sampling"]
+    names += [n for n in ("linear_rows", "attention_decode") if n in build.sources()]
     if dtype == torch.bfloat16:
-        names += [n for n in ("linear_tcgen05", "attention_prefill", "attention_decode") if n in build.sources()]
-        if "linear_rows" in build.sources():
-            names.append("linear_rows")
+        names += [n for n in ("linear_tcgen05", "attention_prefill") if n in build.sources()]
     return names
 
 
@@ -210,15 +209,20 @@ class Ops:
         # set to False to keep the bfloat16 engine on the CUDA-core kernels (tests compare both)
         self.tensor_core_linear = dtype == torch.bfloat16 and "linear_tcgen05" in build.sources()
         self.tensor_core_prefill = dtype == torch.bfloat16 and "attention_prefill" in build.sources()
-        self.fast_decode = dtype == torch.bfloat16 and "attention_decode" in build.sources()
+        self.fast_decode = "attention_decode" in build.sources()        # both dtypes: the decode kernel is templated on the storage type
         # Up to 16 rows the product can also run as a stream of weights through registers on the CUDA cores
         # (linear_rows.cu).  Measured on a B200 it beats the tensor-core kernel at one or two rows (qkv at 1 row:
         # 2.4 us against 3.9 us; a GPT-2 small decode step at batch 1: 0.286 ms against 0.326 ms, at batch 2: 0.314
         # against 0.319) and loses from 4 rows on (batch 4: 0.410 ms against 0.327), and it loses on the output head
         # (50257 outputs: the step is 0.307 ms with it, 0.286 without).  So it takes products of at most
         # `rows_linear_max` rows and `ROWS_LINEAR_MAX_OUT` outputs; form="rows" selects it for any count up to 16.
-        self.rows_linear_max = 2 if dtype == torch.bfloat16 and "linear_rows" in build.sources() else 0
+        # In 32-bit there are no tensor cores to lose to: the weight stream is the decode road of the float32 engine
+        # for every row count it takes (the tiled CUDA-core kernel would run one row in a tile of 64).
+        self.rows_linear_max = (2 if dtype == torch.bfloat16 else 16) if "linear_rows" in build.sources() else 0
         self._counters = None       # zeroed ints the decode kernel counts finished splits in (left zeroed by it)
+        from . import profile
+        if profile.enabled():       # KVAD_PROFILE=1: a table of device time per operation at exit
+            profile.instrument(self)
 
     def path_key(self) -> tuple:
         """Everything on the host that decides which kernels a step of a given shape launches; part of
@@ -290,14 +294,17 @@ class Ops:
             bias_f32 = 1 if bias.dtype == torch.float32 else 0
             if not bias_f32 and bias.dtype != torch.bfloat16:
                 raise KernelError(f"linear: bias must be float32 or bfloat16, not {bias.dtype}")
-        if (self.dtype == torch.bfloat16 and (form == "rows" or (form == "auto" and m <= self.rows_linear_max and n <= self.ROWS_LINEAR_MAX_OUT)) and m <= 16 and k <= 4096 and k % 8 == 0 and lda % 8 == 0
-                and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
+        ve = 8 if self.dtype == torch.bfloat16 else 4          # elements of a 16-byte piece
+        rows_out_ok = self.dtype == torch.float32 or n <= self.ROWS_LINEAR_MAX_OUT
+        if ((form == "rows" or (form == "auto" and m <= self.rows_linear_max and rows_out_ok)) and m <= 16 and k <= 4096
+                and k % ve == 0 and lda % ve == 0 and (1 << max(0, m - 1).bit_length()) * k * a.element_size() <= 200 * 1024
+                and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and "linear_rows" in build.sources()):
             h = lib("linear_rows")
-            _check(h.kvad_linear_rows(_ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k, epi,
+            _check(h.kvad_linear_rows(self.code, _ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k, epi,
                                       _stream()), h)
             return
         if form == "rows":
-            raise KernelError("linear: the weight-streaming form takes bfloat16, at most 16 rows and K a multiple of 8 up to 4096")
+            raise KernelError("linear: the weight-streaming form takes at most 16 rows and K a multiple of a 16-byte piece up to 4096")
         if self.tensor_core_linear and tcgen05_takes(a, weight, out, lda, ldo):
             h = lib("linear_tcgen05")
             _check(h.kvad_linear_tcgen05(_ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k,

@@ -107,6 +107,7 @@ def linear_case(ops, dtype, m, n, k, epilogue, g, *, bias=True, strided=False, b
 def test_linear_cuda_cores(dtype):
     ops = Ops(DT[dtype])
     ops.tensor_core_linear = False
+    ops.rows_linear_max = 0                 # every row count on the tiled kernel
     g = torch.Generator().manual_seed(3)
     # odd shapes of bisand/kvad's own GEMM test (crates/llm/src/tensor.rs:487-500) and larger ones
     for m, n, k in [(9, 13, 7), (8, 16, 4), (5, 32, 1), (6, 8, 9), (1, 1031, 200), (130, 70, 333), (64, 64, 16)]:
@@ -117,21 +118,32 @@ def test_linear_cuda_cores(dtype):
 
 
 def test_linear_is_true_32_bit_and_row_independent():
-    """The 32-bit kernel sums k in order with fused multiply-adds: a row gives the same bits alone and in a batch,
-    and values that a 19-bit (TF32) product would lose survive."""
+    """The 32-bit kernels sum with fused multiply-adds in an order that depends on K only: a row gives the same
+    bits whatever its company, on each of the two roads (at most 16 rows: the weight stream; more: the tiled
+    kernel, 64 x 64 or 128 x 128 tiles); the two roads agree to rounding; and values that a 19-bit (TF32)
+    product would lose survive on both."""
     ops = Ops(torch.float32)
     g = torch.Generator().manual_seed(4)
-    a, w = torch.randn(70, 96, generator=g), torch.randn(50, 96, generator=g)
-    full = torch.empty(70, 50, device="cuda")
-    one = torch.empty(1, 50, device="cuda")
-    ops.linear(dev(a), dev(w), None, full, "store_f32")
-    ops.linear(dev(a[33:34]), dev(w), None, one, "store_f32")
-    assert torch.equal(full[33:34], one)
-    a = torch.full((1, 8), 1.0 + 2.0 ** -20)
-    w = torch.full((1, 8), 1.0 + 2.0 ** -20)
-    out = torch.empty(1, 1, device="cuda")
-    ops.linear(dev(a), dev(w), None, out, "store_f32")
-    assert abs(out.item() - 8 * (1 + 2.0 ** -20) ** 2) < 2e-6        # TF32 would give exactly 8
+    a, w = torch.randn(300, 96, generator=g), torch.randn(6000, 96, generator=g)
+
+    def run(rows):
+        out = torch.empty(len(rows), 6000, device="cuda")
+        ops.linear(dev(a[rows]), dev(w), None, out, "store_f32")
+        return out
+
+    big = run(list(range(300)))                           # 128 x 128 tiles
+    mid = run(list(range(20, 90)))                        # 64 x 64 tiles
+    assert torch.equal(big[33:34], mid[13:14])
+    few, one = run(list(range(30, 39))), run([33])        # the weight stream, 9 rows and 1
+    assert torch.equal(few[3:4], one)
+    # the two roads add in another order: equal to rounding, not to the bit
+    assert ((one - big[33:34]).abs().max() / big[33].abs().max()).item() < 2e-6
+    for m in (1, 40):
+        a1 = torch.full((m, 8), 1.0 + 2.0 ** -20)
+        w1 = torch.full((1, 8), 1.0 + 2.0 ** -20)
+        out = torch.empty(m, 1, device="cuda")
+        ops.linear(dev(a1), dev(w1), None, out, "store_f32")
+        assert abs(out[0, 0].item() - 8 * (1 + 2.0 ** -20) ** 2) < 2e-6        # TF32 would give exactly 8
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 64, 127, 129, 300])
@@ -559,15 +571,19 @@ def test_attention_prefill_finds_one_far_key():
     assert not ops.prefill_takes(256) and not ops.prefill_takes(24)
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
 @pytest.mark.parametrize("m", [1, 2, 3, 4, 7, 8, 13, 16])
-def test_linear_weight_streaming_form(m):
-    """At most 16 rows: a warp per output column, the column's weights held in registers."""
-    ops = Ops(torch.bfloat16)
+def test_linear_weight_streaming_form(m, dtype):
+    """At most 16 rows: a warp per output column, the column's weights held in registers; bfloat16 and true 32-bit."""
+    ops = Ops(DT[dtype])
     g = torch.Generator().manual_seed(400 + m)
-    for n, k in [(768, 768), (1000, 96), (50, 320), (2304, 64), (777, 3072), (50257, 768), (333, 1600), (40, 4096), (9, 8)]:
+    shapes = [(768, 768), (1000, 96), (50, 320), (2304, 64), (777, 3072), (50257, 768), (333, 1600), (40, 4096), (9, 8)]
+    if dtype == "float32":
+        shapes = [(n, k) for n, k in shapes if max(1, 1 << (m - 1).bit_length()) * k * 4 <= 200 * 1024] + [(31, 12)]
+    for n, k in shapes:
         for epi in ("store", "gelu_tanh", "gelu_erf", "residual", "store_f32"):
-            assert linear_case(ops, "bfloat16", m, n, k, epi, g, form="rows") < KTOL["bfloat16"], (m, n, k, epi)
-    assert linear_case(ops, "bfloat16", m, 333, 128, "store", g, bias=False, strided=True, form="rows") < KTOL["bfloat16"]
-    assert linear_case(ops, "bfloat16", m, 333, 128, "residual", g, bias_f32=True, form="rows") < KTOL["bfloat16"]
+            assert linear_case(ops, dtype, m, n, k, epi, g, form="rows") < KTOL[dtype], (m, n, k, epi)
+    assert linear_case(ops, dtype, m, 333, 128, "store", g, bias=False, strided=True, form="rows") < KTOL[dtype]
+    assert linear_case(ops, dtype, m, 333, 128, "residual", g, bias_f32=True, form="rows") < KTOL[dtype]
     with pytest.raises(KernelError, match="at most 16 rows"):
-        linear_case(ops, "bfloat16", 17, 64, 64, "store", g, form="rows")
+        linear_case(ops, dtype, 17, 64, 64, "store", g, form="rows")

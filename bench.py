@@ -10,7 +10,7 @@ after its own prefill and W warm-up steps; `rounds` holds min / median / max); `
 through `Engine.generate`, host token ids in and out every step; `prefill` - one step of 2 x 1024
 prompt tokens; `roofline` - the decode step's bytes (every weight once + the live cache) over its
 time, against the measured copy bandwidth; `points` - decoding at batch 1 and 64, sampled decoding,
-the 32-bit engine, and (with `--points large`) GPT-2 medium's and XL's workloads; `checked` - the
+the 32-bit engine, and GPT-2 medium's and XL's workloads (`--points small` leaves those two out); `checked` - the
 bfloat16 engine's logits at the prompts' ends against the 32-bit engine's on the same weights.
 Weights are random (seeded), token ids uniform-random (seeded): there is no dataset and no
 checkpoint here.
@@ -297,8 +297,9 @@ def main():
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profiling)")
     ap.add_argument("--phase", default="all", choices=["all", "prefill"], help="`prefill`: only the 2 x 1024-token prefill (profiling)")
-    ap.add_argument("--points", default="default", choices=["none", "default", "large"],
-                    help="`none`: only the headline; `large`: also GPT-2 medium's and XL's workloads (minutes: 0.7 and 3.1 GB of weights)")
+    ap.add_argument("--points", default="large", choices=["none", "small", "large"],
+                    help="`none`: only the headline; `small`: GPT-2 small's other points; `large` (default): also GPT-2 medium's and "
+                         "XL's workloads (0.7 and 3.1 GB of random weights: about half a minute more)")
     ap.add_argument("--skip-points", action="store_true", help="the same as --points none")
     ap.add_argument("--sampling", default="greedy", choices=["greedy", "sampled"],
                     help="`sampled`: the timed decode steps draw with temperature 0.7, top-k 40, top-p 0.95")

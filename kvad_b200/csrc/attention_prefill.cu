@@ -270,6 +270,7 @@ int launch(const void* q, int64_t ld_q, void* out, int64_t ld_out, const int* se
 }
 
 bool g_force_legacy = false;      // tests: keep every head size on the mma.sync kernel
+int g_split_above = 0;            // tests: the tcgen05 kernel's page count above which a tile goes to both slots (0: its own)
 
 // A [rows, cols] bfloat16 matrix with row stride ld, loaded in boxes of box_rows x 64 with the 128-byte swizzle.
 int tile_map(const void* ptr, int64_t ld, int64_t rows, int cols, int box_rows, CUtensorMap* out) {
@@ -328,11 +329,12 @@ int launch_tc(const void* q, int64_t ld_q, int n_rows, void* out, int64_t ld_out
   if (rc != KVAD_OK) return rc;
   rc = tile_map(v_pages, HD, n_pages * n_kv_heads * pftc::KEYS, HD, pftc::KEYS, &mv);
   if (rc != KVAD_OK) return rc;
+  // a CTA takes one long tile or two short ones, which it finds out from the sequence's length: at most a CTA a tile,
+  // and the CTAs left over return at once
   const int n_q_tiles = (max_new + pftc::ROWS - 1) / pftc::ROWS;
-  const int n_pairs = (n_q_tiles + 1) / 2;        // a CTA takes a late tile and an early one
-  kvad_launch(pftc::attention_prefill_tc_kernel<HD>, dim3(n_pairs, n_heads, n_seqs), dim3(pftc::THREADS), L::SMEM, stream,
+  kvad_launch(pftc::attention_prefill_tc_kernel<HD>, dim3(n_q_tiles, n_heads, n_seqs), dim3(pftc::THREADS), L::SMEM, stream,
               mq, mk, mv, (__nv_bfloat16*)out, ld_out, seq_starts, kv_lens, page_table, table_width, n_heads, n_kv_heads,
-              n_q_tiles, scale, window);
+              g_split_above > 0 ? g_split_above : pftc::SPLIT_ABOVE, scale, window);
   KVAD_CHECK_LAUNCH("attention_prefill_tc");
   return KVAD_OK;
 }
@@ -341,6 +343,10 @@ int launch_tc(const void* q, int64_t ld_q, int n_rows, void* out, int64_t ld_out
 
 // Tests: 1 keeps head sizes 64 and 128 on the mma.sync kernel too.
 KVAD_EXPORT void kvad_attention_prefill_force_legacy(int on) { g_force_legacy = on != 0; }
+
+// Tests and measurements: from how many pages on (exclusive) the tcgen05 kernel gives a tile of rows to both of a
+// CTA's slots, half of the pages each; 0: the kernel's own choice.
+KVAD_EXPORT void kvad_attention_prefill_split_above(int pages) { g_split_above = pages; }
 
 // How many bounded waits of the tcgen05 kernel have run out since the library was loaded (0 in a healthy run).
 KVAD_EXPORT int kvad_attention_prefill_status() {

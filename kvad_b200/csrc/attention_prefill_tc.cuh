@@ -1,11 +1,15 @@
 // Causal attention of prompt rows on the 5th-generation tensor cores (head sizes 64 and 128).
 //
-// A CTA serves two tiles of 128 consecutive rows of one sequence and one head (a late tile of the prompt
-// paired with an early one, so that CTAs have like amounts of work) and walks the sequence's cache pages
-// (64 keys each).  Roles: warp 0 brings Q once and a ring of K/V pages by TMA (128-byte swizzle); one
-// thread of warp 1 issues tcgen05.mma; warps 2-5 are the softmax of the first tile and warps 6-9 of the
-// second, one thread per row.  (A kernel that allocates tensor memory gets one CTA per SM, whatever else
-// it needs: the second tile is what keeps the tensor core busy while the first one's softmax runs.)
+// A CTA has two SLOTS, each a group of four softmax warps (a thread per row) with its own S, P and P.V
+// buffers, that walk cache pages (64 keys each) side by side.  What limits the kernel is the chain
+// through one softmax thread - ~0.9 us a page - so the work is cut to keep every chain short: a tile of
+// 128 rows that sees more than 8 pages is given to BOTH slots, each walking half of its pages, and
+// the halves (unnormalised output, maximum, sum) meet through shared memory at the end; shorter
+// tiles go two to a CTA, a longer one paired with a shorter one.  Roles: warp 0 brings Q and a ring of
+// K/V pages by TMA (128-byte swizzle), in the order the slots use them (a page both slots read at the
+// same step is brought once); one thread of warp 1 issues tcgen05.mma; warps 2-5 are slot 0, warps 6-9
+// slot 1.  (A kernel that allocates tensor memory gets one CTA per SM, whatever else it needs: the
+// second slot is what keeps the tensor core busy while the first one's softmax runs.)
 //
 //   S_i = Q . K_i^T        128 x 64 in tensor memory, two buffers
 //   softmax thread r       reads row r of S_i with tcgen05.ld, scales and masks it, keeps the row's running
@@ -28,14 +32,15 @@
 namespace kvad {
 namespace pftc {
 
-constexpr int ROWS = 128;         // query rows per tile; a CTA serves two tiles
-constexpr int TILES = 2;
+constexpr int ROWS = 128;         // query rows per tile
+constexpr int TILES = 2;          // slots of a CTA
+constexpr int SPLIT_ABOVE = 8;    // a tile that sees more pages than this is walked by both slots, half each (the launch may say otherwise)
 constexpr int KEYS = 64;          // keys per step = one cache page
 constexpr int THREADS = 64 + TILES * 128;
 
 template <int HD> struct Layout {
   static constexpr int KB = HD / 64;                          // 64-wide blocks of the head dimension
-  static constexpr int STAGES = HD == 64 ? 4 : 3;
+  static constexpr int STAGES = HD == 64 ? 6 : 3;             // pages in the ring; two slots on pages of their own use two a step
   static constexpr int T_BUFS = HD == 64 ? 2 : 1;             // buffers of P.V per tile in tensor memory
   static constexpr uint32_t Q_BYTES = ROWS * HD * 2;          // one tile's rows
   static constexpr uint32_t TILE_BYTES = KEYS * HD * 2;       // K or V of one page and head
@@ -97,7 +102,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 __device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// Which pages tile `t` of a CTA walks.
+// Which pages slot `t` of a CTA walks, for which tile.
 struct TileRange {
   int qt;            // index of the 128-row tile within the sequence's new rows; -1: none
   int rows;          // rows of it that exist
@@ -111,7 +116,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, int64_t ld_out,
                             const int* __restrict__ seq_starts, const int* __restrict__ kv_lens,
                             const int* __restrict__ page_table, int table_width, int n_heads, int n_kv_heads,
-                            int n_q_tiles, float scale, int window) {
+                            int split_above, float scale, int window) {
   using L = Layout<HD>;
   constexpr int STAGES = L::STAGES, T_BUFS = L::T_BUFS;
   extern __shared__ uint8_t pftc_raw[];
@@ -130,12 +135,81 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Which tiles this CTA serves is decided first, from the step's metadata (uploaded before the step's first
+  // kernel, so readable before the dependent-launch wait): a CTA with nothing to do leaves before it has
+  // set anything up.
+  const int s = blockIdx.z, h = blockIdx.y;
+  const int row0_seq = seq_starts[s];
+  const int n_new = seq_starts[s + 1] - row0_seq;
+  const int kv_len = kv_lens[s];
+  const int first_pos = kv_len - n_new;
+  const int kvh = h / (n_heads / n_kv_heads);
+  const int* pages = page_table + (int64_t)s * table_width;
+  const int n_tiles_seq = (n_new + ROWS - 1) / ROWS;
+  auto tile_range = [&](int qt, TileRange& r) {
+    r.qt = qt;
+    r.rows = (n_new - qt * ROWS) < ROWS ? (n_new - qt * ROWS) : ROWS;
+    r.pos0 = first_pos + qt * ROWS;
+    r.j_hi = (r.pos0 + r.rows - 1) / KEYS;
+    r.j_lo = 0;
+    if (window > 0 && r.pos0 - window + 1 > 0) r.j_lo = (r.pos0 - window + 1) / KEYS;
+  };
+  TileRange tr[TILES];
+  tr[0].qt = tr[1].qt = -1;
+  tr[0].rows = tr[1].rows = 0;
+  tr[0].pos0 = tr[1].pos0 = first_pos;
+  tr[0].j_lo = tr[1].j_lo = 0x3fffffff;
+  tr[0].j_hi = tr[1].j_hi = -1;
+  bool split = false;
+  {
+    // CTAs 0 .. n_split-1 take the tiles that see more than `split_above` pages, latest first, both slots on one tile;
+    // the CTAs after them pair the other tiles, the c-th latest with the c-th earliest.
+    int n_split = 0;
+    for (int qt = 0; qt < n_tiles_seq; ++qt) {
+      TileRange r;
+      tile_range(qt, r);
+      n_split += (r.j_hi - r.j_lo + 1 > split_above) ? 1 : 0;
+    }
+    const int c = (int)blockIdx.x, n_rest = n_tiles_seq - n_split;
+    const int want_a = c < n_split ? c : c - n_split;                      // how many tiles of its kind come before, latest first
+    const int want_b = c < n_split ? -1 : n_rest - 1 - (c - n_split);
+    int seen = 0;
+    for (int qt = n_tiles_seq - 1; qt >= 0; --qt) {
+      TileRange r;
+      tile_range(qt, r);
+      const bool is_split = r.j_hi - r.j_lo + 1 > split_above;
+      if (is_split != (c < n_split)) continue;
+      if (seen == want_a && (c < n_split || want_b >= want_a)) tr[0] = r;
+      if (seen == want_b && want_b > want_a) tr[1] = r;
+      ++seen;
+    }
+    if (c < n_split && tr[0].qt >= 0) {
+      split = true;
+      tr[1] = tr[0];
+      const int mid = tr[0].j_lo + (tr[0].j_hi - tr[0].j_lo + 2) / 2;      // slot 0: the earlier pages; slot 1: the later ones, with the diagonal
+      tr[0].j_hi = mid - 1;
+      tr[1].j_lo = mid;
+    }
+  }
+  const bool active = tr[0].qt >= 0;
+  if (!active) return;
+  const int n_steps0 = tr[0].j_hi - tr[0].j_lo + 1, n_steps1 = tr[1].qt >= 0 ? tr[1].j_hi - tr[1].j_lo + 1 : 0;
+  const int n_steps_max = n_steps0 > n_steps1 ? n_steps0 : n_steps1;
+  // The ring holds pages in the order of use: step by step, slot 0's page, then slot 1's unless it is the same one
+  // (two tiles that start at the same page walk it together).  load_of(t, i): which load serves slot t at step i.
+  const bool same_start = !split && tr[1].qt >= 0 && tr[0].j_lo == tr[1].j_lo;      // then slot 1 (the earlier tile) has no more steps than slot 0
+  auto load_of = [&](int t, int i) -> int {
+    if (same_start) return i;
+    const int a = i < n_steps0 ? i : n_steps0, b = i < n_steps1 ? i : n_steps1;
+    return a + b + ((t == 1 && i < n_steps0) ? 1 : 0);
+  };
+
   if (threadIdx.x == 0) {
     prefetch_tensormap(&map_q);
     prefetch_tensormap(&map_k);
     prefetch_tensormap(&map_v);
     mbar_init(q_full, 1);
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int st = 0; st < STAGES; ++st) { mbar_init(&kv_full[st], 1); mbar_init(&kv_empty[st], 1); }
     for (int b = 0; b < TILES * 2; ++b) {
       mbar_init(&s_full[b], 1);
       mbar_init(&p_full[b], 128);
@@ -152,110 +226,99 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const uint32_t tmem_base = *tmem_slot;
 
   pdl_wait();                                      // everything below reads what earlier kernels of the step wrote
-  const int s = blockIdx.z, h = blockIdx.y;
-  const int row0_seq = seq_starts[s];
-  const int n_new = seq_starts[s + 1] - row0_seq;
-  const int kv_len = kv_lens[s];
-  const int first_pos = kv_len - n_new;
-  const int kvh = h / (n_heads / n_kv_heads);
-  const int* pages = page_table + (int64_t)s * table_width;
-  // a CTA pairs a late tile of the sequence (many pages) with an early one (few), so that all CTAs of a
-  // sequence walk about the same number of pages; both read the pages they share from one copy
-  const int n_tiles_seq = (n_new + ROWS - 1) / ROWS;
-  TileRange tr[TILES];
-  {
-    const int c = (int)blockIdx.x;
-    const int heavy = n_tiles_seq - 1 - c, light = c;
-    const int which[TILES] = {heavy, (light < heavy) ? light : -1};
-#pragma unroll
-    for (int t = 0; t < TILES; ++t) {
-      const int qt = (heavy >= 0 && heavy >= light) ? which[t] : -1;
-      tr[t].qt = qt;
-      tr[t].rows = qt < 0 ? 0 : ((n_new - qt * ROWS) < ROWS ? (n_new - qt * ROWS) : ROWS);
-      tr[t].pos0 = first_pos + (qt < 0 ? 0 : qt) * ROWS;
-      tr[t].j_hi = qt < 0 ? -1 : (tr[t].pos0 + tr[t].rows - 1) / KEYS;
-      tr[t].j_lo = 0;
-      if (window > 0 && tr[t].pos0 - window + 1 > 0) tr[t].j_lo = (tr[t].pos0 - window + 1) / KEYS;
-      if (qt < 0) tr[t].j_lo = 0x3fffffff;
-    }
-  }
-  const bool active = tr[0].qt >= 0;
-  const int lo_all = tr[0].j_lo < tr[1].j_lo ? tr[0].j_lo : tr[1].j_lo;
-  const int hi_all = tr[0].j_hi > tr[1].j_hi ? tr[0].j_hi : tr[1].j_hi;
-  // (pages between the two tiles' ranges, which a window can leave, are loaded and skipped by both)
 
   if (warp == 0) {
-    if (lane == 0 && active) {
-      mbar_expect_tx(q_full, (tr[1].qt >= 0 ? 2 : 1) * L::Q_BYTES);
+    if (lane == 0) {
+      const int n_q = (tr[1].qt >= 0 && !split) ? 2 : 1;                   // both slots of a split tile read one copy of its rows
+      mbar_expect_tx(q_full, n_q * L::Q_BYTES);
 #pragma unroll
       for (int t = 0; t < TILES; ++t)
-        if (tr[t].qt >= 0)
+        if (t < n_q)
           for (int kb = 0; kb < L::KB; ++kb)
             tma_load_2d(q_tiles + t * L::Q_BYTES + kb * (ROWS * 128), &map_q, q_full, h * HD + kb * 64, row0_seq + tr[t].qt * ROWS);
-      for (int j = lo_all; j <= hi_all; ++j) {
-        const int i = j - lo_all, st = i % STAGES;
-        if (i >= STAGES && !mbar_wait(&kv_empty[st], ((i / STAGES) & 1) ^ 1)) break;
-        uint8_t* k_dst = kv_tiles + st * 2 * L::TILE_BYTES;
-        uint8_t* v_dst = k_dst + L::TILE_BYTES;
-        const int y = (pages[j] * n_kv_heads + kvh) * KEYS;
-        mbar_expect_tx(&kv_full[st], 2 * L::TILE_BYTES);
+      int li = 0;
+      bool ok = true;
+      for (int i = 0; i < n_steps_max && ok; ++i) {
 #pragma unroll
-        for (int kb = 0; kb < L::KB; ++kb) {
-          tma_load_2d(k_dst + kb * (KEYS * 128), &map_k, &kv_full[st], kb * 64, y);
-          tma_load_2d(v_dst + kb * (KEYS * 128), &map_v, &kv_full[st], kb * 64, y);
+        for (int t = 0; t < TILES; ++t) {
+          if (i >= (t == 0 ? n_steps0 : n_steps1) || (t == 1 && same_start)) continue;
+          const int st = li % STAGES;
+          if (li >= STAGES && !mbar_wait(&kv_empty[st], ((li / STAGES) & 1) ^ 1)) { ok = false; break; }
+          uint8_t* k_dst = kv_tiles + st * 2 * L::TILE_BYTES;
+          uint8_t* v_dst = k_dst + L::TILE_BYTES;
+          const int y = (pages[tr[t].j_lo + i] * n_kv_heads + kvh) * KEYS;
+          mbar_expect_tx(&kv_full[st], 2 * L::TILE_BYTES);
+#pragma unroll
+          for (int kb = 0; kb < L::KB; ++kb) {
+            tma_load_2d(k_dst + kb * (KEYS * 128), &map_k, &kv_full[st], kb * 64, y);
+            tma_load_2d(v_dst + kb * (KEYS * 128), &map_v, &kv_full[st], kb * 64, y);
+          }
+          ++li;
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && active) {
+    if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_instr_desc(ROWS, KEYS);
       constexpr uint32_t idesc_pv = umma_instr_desc(ROWS, HD, false, true);
       bool ok = mbar_wait(q_full, 0);
-      // per page: S of both tiles, then P.V of the page before for both, so that the first product of a page is
-      // under way while the softmax threads are on the page before
-      for (int j = lo_all; j <= hi_all + 1 && ok; ++j) {
-        const int i = j - lo_all;
-        if (j <= hi_all) {
-          const int st = i % STAGES;
-          ok = mbar_wait(&kv_full[st], (i / STAGES) & 1);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t k_addr = smem_u32(kv_tiles + st * 2 * L::TILE_BYTES);
+      // Per step: S of both slots, then P.V of the step before for both, so that the first product of a step is
+      // under way while the softmax threads are on the step before.  With a ring of fewer than four pages (head size
+      // 128) and two slots on pages of their own that order would need a fourth page: there each slot's S is followed
+      // at once by its P.V of the step before, which gives the page back.
+      constexpr bool INTERLEAVE = STAGES < 4;
+      auto product_s = [&](int t, int i) {
+        const int ld = load_of(t, i), st = ld % STAGES, b = i & 1;
+        if (!mbar_wait(&kv_full[st], (ld / STAGES) & 1)) { ok = false; return; }
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(kv_tiles + st * 2 * L::TILE_BYTES);
+        const uint32_t q_addr = smem_u32(q_tiles + (split ? 0 : t) * L::Q_BYTES);
 #pragma unroll
-          for (int t = 0; t < TILES; ++t) {
-            if (j < tr[t].j_lo || j > tr[t].j_hi) continue;
-            const int k_step = j - tr[t].j_lo, b = k_step & 1;
-            const uint32_t q_addr = smem_u32(q_tiles + t * L::Q_BYTES);
-#pragma unroll
-            for (int k = 0; k < HD / 16; ++k) {
-              const uint64_t a_desc = sw128_desc(q_addr + (k / 4) * (ROWS * 128)) + (uint64_t)((k % 4) * 2);
-              const uint64_t b_desc = sw128_desc(k_addr + (k / 4) * (KEYS * 128)) + (uint64_t)((k % 4) * 2);
-              umma(tmem_base + t * L::TMEM_TILE + b * KEYS, a_desc, b_desc, idesc_qk, k > 0 ? 1u : 0u);
-            }
-            umma_commit(&s_full[t * 2 + b]);
-          }
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint64_t a_desc = sw128_desc(q_addr + (k / 4) * (ROWS * 128)) + (uint64_t)((k % 4) * 2);
+          const uint64_t b_desc = sw128_desc(k_addr + (k / 4) * (KEYS * 128)) + (uint64_t)((k % 4) * 2);
+          umma(tmem_base + t * L::TMEM_TILE + b * KEYS, a_desc, b_desc, idesc_qk, k > 0 ? 1u : 0u);
         }
-        if (j > lo_all) {
-          const int jp = j - 1, st = (jp - lo_all) % STAGES;
-          const uint32_t v_addr = smem_u32(kv_tiles + st * 2 * L::TILE_BYTES + L::TILE_BYTES);
+        umma_commit(&s_full[t * 2 + b]);
+      };
+      auto product_pv = [&](int t, int ip) {
+        const int st = load_of(t, ip) % STAGES, b = ip & 1, tb = ip % T_BUFS;
+        const uint32_t v_addr = smem_u32(kv_tiles + st * 2 * L::TILE_BYTES + L::TILE_BYTES);
+        if (!(mbar_wait(&p_full[t * 2 + b], (ip >> 1) & 1) && mbar_wait(&t_empty[t * 2 + tb], ((ip / T_BUFS) & 1) ^ 1))) { ok = false; return; }
+        tc_fence_after();
+        const uint32_t p_addr = smem_u32(p_tiles + (t * 2 + b) * L::P_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < KEYS / 16; ++kk) {
+          const uint64_t a_desc = sw128_desc(p_addr) + (uint64_t)(kk * 2);
+          const uint64_t b_desc = sw128_mn_desc(v_addr + kk * 2048, KEYS * 128);
+          umma(tmem_base + t * L::TMEM_TILE + L::TMEM_T + tb * HD, a_desc, b_desc, idesc_pv, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&t_full[t * 2 + tb]);
+      };
+      const int n_steps_of[TILES] = {n_steps0, n_steps1};
+      for (int i = 0; i <= n_steps_max && ok; ++i) {
+        if (INTERLEAVE && !same_start) {
 #pragma unroll
           for (int t = 0; t < TILES; ++t) {
-            if (jp < tr[t].j_lo || jp > tr[t].j_hi) continue;
-            const int k_step = jp - tr[t].j_lo, b = k_step & 1, tb = k_step % T_BUFS;
-            ok = ok && mbar_wait(&p_full[t * 2 + b], (k_step >> 1) & 1) &&
-                 mbar_wait(&t_empty[t * 2 + tb], ((k_step / T_BUFS) & 1) ^ 1);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t p_addr = smem_u32(p_tiles + (t * 2 + b) * L::P_BYTES);
-#pragma unroll
-            for (int kk = 0; kk < KEYS / 16; ++kk) {
-              const uint64_t a_desc = sw128_desc(p_addr) + (uint64_t)(kk * 2);
-              const uint64_t b_desc = sw128_mn_desc(v_addr + kk * 2048, KEYS * 128);
-              umma(tmem_base + t * L::TMEM_TILE + L::TMEM_T + tb * HD, a_desc, b_desc, idesc_pv, kk > 0 ? 1u : 0u);
+            if (i < n_steps_of[t] && ok) product_s(t, i);
+            if (i > 0 && i - 1 < n_steps_of[t] && ok) {
+              product_pv(t, i - 1);
+              if (ok) umma_commit(&kv_empty[load_of(t, i - 1) % STAGES]);      // the page has been read
             }
-            umma_commit(&t_full[t * 2 + tb]);
           }
-          umma_commit(&kv_empty[st]);               // the page's K and V have been read by all that use them
+        } else {
+#pragma unroll
+          for (int t = 0; t < TILES; ++t)
+            if (i < n_steps_of[t] && ok) product_s(t, i);
+          if (i > 0) {
+#pragma unroll
+            for (int t = 0; t < TILES; ++t)
+              if (i - 1 < n_steps_of[t] && ok) product_pv(t, i - 1);
+            // the step's pages have been read by all that use them
+#pragma unroll
+            for (int t = 0; t < TILES; ++t)
+              if (ok && i - 1 < n_steps_of[t] && !(t == 1 && same_start)) umma_commit(&kv_empty[load_of(t, i - 1) % STAGES]);
+          }
         }
       }
     }
@@ -345,8 +408,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // (both tiles may clear the same rows; they write the same zeros)
       const int valid = kv_len - j * KEYS;
       if (valid < KEYS) {
-        const int i = j - lo_all, st = i % STAGES;
-        if (!mbar_wait(&kv_full[st], (i / STAGES) & 1)) { ok = false; break; }
+        const int ld = load_of(t, k), st = ld % STAGES;
+        if (!mbar_wait(&kv_full[st], (ld / STAGES) & 1)) { ok = false; break; }
         uint8_t* v_tile = kv_tiles + st * 2 * L::TILE_BYTES + L::TILE_BYTES;
         const int first = valid < 0 ? 0 : valid;
         const int n16 = (KEYS - first) * 8;                          // 16-byte pieces of the rows to clear, per 64-wide block
@@ -361,7 +424,30 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       keep_prev = keep;
     }
     if (ok && n_steps > 0) take_product(n_steps - 1, keep_prev);
-    if (ok && row < me.rows) {
+    if (split) {
+      // The two halves of the tile meet: all products of the CTA have been read (each slot has taken its last one),
+      // so the page ring is free; slot 1 leaves its rows' sums, maxima and unnormalised outputs there, slot 0 adds.
+      float* xch = reinterpret_cast<float*>(kv_tiles);                      // [ROWS][HD + 2]
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      if (t == 1) {
+        float* mine = xch + row * (HD + 2);
+#pragma unroll
+        for (int c = 0; c < HD; ++c) mine[c] = o[c];
+        mine[HD] = run_max;
+        mine[HD + 1] = run_sum;
+      }
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      if (t == 0) {
+        const float* other = xch + row * (HD + 2);
+        const float m1 = other[HD], l1 = other[HD + 1];
+        const float m = fmaxf(run_max, m1);
+        const float s0 = run_max == -INFINITY ? 0.f : fast_exp2(run_max - m), s1 = m1 == -INFINITY ? 0.f : fast_exp2(m1 - m);
+        run_sum = run_sum * s0 + l1 * s1;
+#pragma unroll
+        for (int c = 0; c < HD; ++c) o[c] = o[c] * s0 + other[c] * s1;
+      }
+    }
+    if (ok && row < me.rows && !(split && t == 1)) {
       const float inv = 1.0f / run_sum;
       __nv_bfloat16* dst = out + (int64_t)(row0_seq + me.qt * ROWS + row) * ld_out + (int64_t)h * HD;
 #pragma unroll

@@ -53,6 +53,7 @@ constexpr int SMEM_BUDGET = 200 * 1024;
 constexpr int SMEM_BUDGET_WIDE = 192 * 1024;     // the wide form keeps 33 KB for its output slabs
 
 bool g_no_3d = false;               // tests: keep the swapped form on one TMA load per K block
+bool g_test_skip_load = false;      // tests: the next launch of the swapped form (one load per K block) leaves out its first load
 bool g_no_cluster_k = false;        // tests: never split K over a cluster under a storing epilogue
 bool g_no_tma_out = false;          // tests: the wide form writes its output with plain stores
 bool g_force_3d = false;            // tests: take the grouped three-dimensional loads at every row count
@@ -400,10 +401,12 @@ template <int MB, int TM> struct SkinnyTile {
 template <int MB, int EPI, int TM>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 linear_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                             const void* __restrict__ bias, int bias_f32, void* __restrict__ out, int64_t ldo,
+                             const void* __restrict__ bias, int bias_flags, void* __restrict__ out, int64_t ldo,
                              int M, int N, int K, int kb_per_split) {
   using T = SkinnyTile<MB, TM>;
   constexpr int STAGES = T::STAGES;
+  const int bias_f32 = bias_flags & 1;
+  const bool test_skip_first_load = (bias_flags & 2) != 0;     // a test's way to make a bounded wait run out: nothing ever fills stage 0
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* w_tiles = smem;
@@ -444,12 +447,12 @@ linear_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __
     if (lane == 0) {
       // this CTA's weights (often all of them) are requested before the kernel before has finished
       const int pre = num_kb < STAGES ? num_kb : STAGES;
-      for (int i = 0; i < pre; ++i) {
+      for (int i = test_skip_first_load ? 1 : 0; i < pre; ++i) {
         mbar_expect_tx(&full_bar[i], T::W_BYTES + T::A_BYTES);
         tma_load_2d(w_tiles + i * T::W_BYTES, &map_w, &full_bar[i], (kb_begin + i) * BK, n0);
       }
       pdl_wait();
-      for (int i = 0; i < pre; ++i)
+      for (int i = test_skip_first_load ? 1 : 0; i < pre; ++i)
         tma_load_2d(a_tiles + i * T::A_BYTES, &map_a, &full_bar[i], (kb_begin + i) * BK, 0);
       for (int i = pre; i < num_kb; ++i) {
         const int s = i % STAGES;
@@ -898,7 +901,9 @@ int launch_skinny(const CUtensorMap& ma, const CUtensorMap& mw, const void* bias
   const int kb_per_split = (kb_total + splits - 1) / splits;
   const int z = (kb_total + kb_per_split - 1) / kb_per_split;
   dim3 grid((N + TM - 1) / TM, z);
-  kvad_launch(linear_tcgen05_skinny_kernel<MB, EPI, TM>, grid, dim3(NUM_THREADS), T::SMEM, stream, ma, mw, bias, bias_f32, out, ldo, M, N, K, kb_per_split);
+  const int test_skip = g_test_skip_load ? 2 : 0;       // rides in a free bit of bias_f32
+  g_test_skip_load = false;
+  kvad_launch(linear_tcgen05_skinny_kernel<MB, EPI, TM>, grid, dim3(NUM_THREADS), T::SMEM, stream, ma, mw, bias, bias_f32 | test_skip, out, ldo, M, N, K, kb_per_split);
   KVAD_CHECK_LAUNCH("linear_tcgen05_skinny");
   return KVAD_OK;
 }
@@ -1106,6 +1111,18 @@ KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, c
 // Tests: 1 keeps the swapped form on two-dimensional loads (one per K block) for every K; 2 takes the
 // grouped three-dimensional loads whenever K allows; 0 is the kernel's own choice (them, up to 16 rows).
 KVAD_EXPORT void kvad_linear_tcgen05_no_3d(int on) { g_no_3d = on == 1; g_force_3d = on == 2; }
+
+// Tests of the bounded waits: `wait_limit` > 0 sets how many polls a wait makes before it gives up (0: the
+// library's own limit); `skip_first_load` makes the NEXT launch of the swapped form with one load per K block
+// leave out its first load, so that the wait for it runs out: the launch raises the status counter, writes
+// an output that means nothing, frees its tensor memory and returns; launches after it are ordinary.
+KVAD_EXPORT int kvad_linear_tcgen05_test_hooks(unsigned wait_limit, int skip_first_load) {
+  const uint32_t limit = wait_limit > 0 ? wait_limit : WAIT_LIMIT;
+  cudaError_t e = cudaMemcpyToSymbol(g_wait_limit, &limit, sizeof(limit));
+  if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "linear_tcgen05: cannot set the wait limit: %s", cudaGetErrorString(e));
+  g_test_skip_load = skip_first_load != 0;
+  return KVAD_OK;
+}
 
 // Tests: 1 makes the wide form write its output with plain stores instead of TMA stores / reduce-adds.
 KVAD_EXPORT void kvad_linear_tcgen05_no_tma_out(int on) { g_no_tma_out = on != 0; }

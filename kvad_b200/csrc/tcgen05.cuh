@@ -14,6 +14,8 @@ namespace kvad {
 
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 static __device__ int g_wait_timeouts = 0;
+// polls a bounded wait makes before it gives up (a test may shorten it to see a wait run out)
+static __device__ uint32_t g_wait_limit = WAIT_LIMIT;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -35,9 +37,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded: gives up after WAIT_LIMIT polls and says so.
+// Bounded: gives up after g_wait_limit polls and says so.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint32_t limit = g_wait_limit;
+  for (uint32_t i = 1; i < limit; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   atomicAdd(&g_wait_timeouts, 1);
   return false;

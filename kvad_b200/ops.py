@@ -477,6 +477,16 @@ def prefill_force_legacy(on: bool) -> None:
     h.kvad_attention_prefill_force_legacy(int(bool(on)))
 
 
+def prefill_split_above(pages: int) -> None:
+    """Tests and measurements: the tensor-core prompt attention gives a tile of 128 rows to both slots of a CTA,
+    half of its pages each, when it sees more than `pages` pages (0: the kernel's own choice, 8)."""
+    h = lib("attention_prefill")
+    h.kvad_attention_prefill_split_above.argtypes = [c_int]
+    h.kvad_attention_prefill_split_above.restype = None
+    h.kvad_attention_prefill_split_above(int(pages))
+    switches_changed()
+
+
 def prefill_wait_timeouts() -> int:
     """How many bounded waits of the tcgen05 prompt attention have run out (0 in a healthy run)."""
     h = lib("attention_prefill")
@@ -535,6 +545,17 @@ def tcgen05_plain_stores(on: bool) -> None:
     h.kvad_linear_tcgen05_no_tma_out.argtypes = [c_int]
     h.kvad_linear_tcgen05_no_tma_out.restype = None
     h.kvad_linear_tcgen05_no_tma_out(int(bool(on)))
+
+
+def tcgen05_test_hooks(wait_limit: int = 0, skip_first_load: bool = False) -> None:
+    """Tests of the bounded waits of the tensor-core linear kernel: `wait_limit` polls before a wait gives up
+    (0: the library's own limit); `skip_first_load`: the next launch of the swapped form (17..64 rows) leaves
+    out its first load, so its wait for it runs out and the launch returns with the status counter raised."""
+    h = lib("linear_tcgen05")
+    h.kvad_linear_tcgen05_test_hooks.argtypes = [ctypes.c_uint, c_int]
+    h.kvad_linear_tcgen05_test_hooks.restype = c_int
+    if h.kvad_linear_tcgen05_test_hooks(int(wait_limit), int(bool(skip_first_load))) != 0:
+        raise KernelError(h.kvad_last_error().decode("utf-8", "replace"))
 
 
 def tcgen05_wait_timeouts() -> int:

@@ -512,19 +512,22 @@ def test_attention_decode_finds_one_far_key():
 
 @pytest.mark.parametrize("hd,n_heads,n_kv,window", [(16, 4, 4, 0), (32, 3, 3, 0), (48, 6, 2, 0), (64, 12, 12, 0), (80, 3, 1, 0),
                                                     (96, 2, 2, 0), (112, 2, 1, 0), (128, 2, 2, 50), (64, 4, 2, 70), (32, 5, 5, 64)])
-@pytest.mark.parametrize("form", ["auto", "mma.sync"])
+@pytest.mark.parametrize("form", ["auto", "mma.sync", "split"])
 def test_attention_prefill_tensor_cores(hd, n_heads, n_kv, window, form):
     """Whole prompts, prompts that continue cached positions, a single row and a row count that is no multiple
     of the tile, in one launch; the pages hold NaN wherever no position lies.  Head sizes 64 and 128 run on
-    tcgen05 unless the older mma.sync kernel is forced."""
-    from kvad_b200.ops import prefill_force_legacy, prefill_wait_timeouts
-    if form == "mma.sync" and hd not in (64, 128):
+    tcgen05 unless the older mma.sync kernel is forced.  "split": every tile of rows that sees two pages or more is
+    walked by both slots of its CTA, half of the pages each (by itself the kernel does that from nine pages on)."""
+    from kvad_b200.ops import prefill_force_legacy, prefill_split_above, prefill_wait_timeouts
+    if form != "auto" and hd not in (64, 128):
         pytest.skip("this head size has one kernel only")
     prefill_force_legacy(form == "mma.sync")
+    prefill_split_above(1 if form == "split" else 0)
     try:
         _attention_prefill_case(hd, n_heads, n_kv, window)
     finally:
         prefill_force_legacy(False)
+        prefill_split_above(0)
     assert prefill_wait_timeouts() == 0
 
 
@@ -587,3 +590,30 @@ def test_linear_weight_streaming_form(m, dtype):
     assert linear_case(ops, dtype, m, 333, 128, "residual", g, bias_f32=True, form="rows") < KTOL[dtype]
     with pytest.raises(KernelError, match="at most 16 rows"):
         linear_case(ops, dtype, 17, 64, 64, "store", g, form="rows")
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_harmless():
+    """A load that never comes: the launch's wait for it runs out after the (shortened) limit, the status counter
+    says so, the launch frees what it holds and returns - and the next, ordinary launch is right.  Nothing here
+    faults or hangs: the kernel is told to leave out one load, and its wait gives up by counting."""
+    from kvad_b200.ops import tcgen05_test_hooks, tcgen05_wait_timeouts
+    ops = Ops(torch.bfloat16)
+    if not ops.tensor_core_linear:
+        pytest.skip("no tensor-core linear kernel")
+    g = torch.Generator().manual_seed(9)
+    assert linear_case(ops, "bfloat16", 32, 128, 128, "store", g, form="swapped") < KTOL["bfloat16"]
+    before = tcgen05_wait_timeouts()
+    a = dev(torch.randn(32, 128, generator=g).bfloat16())
+    w = dev((torch.randn(128, 128, generator=g) / 11).bfloat16())
+    out = torch.zeros(32, 128, device="cuda", dtype=torch.bfloat16)
+    try:
+        tcgen05_test_hooks(wait_limit=4096, skip_first_load=True)
+        ops.linear(a, w, None, out, "store", form="swapped")          # one CTA; stage 0 is never filled
+        torch.cuda.synchronize()                                       # returns: no hang
+        assert tcgen05_wait_timeouts() > before
+    finally:
+        tcgen05_test_hooks(0, False)
+    again = tcgen05_wait_timeouts()
+    assert linear_case(ops, "bfloat16", 32, 128, 128, "store", g, form="swapped") < KTOL["bfloat16"]
+    assert linear_case(ops, "bfloat16", 300, 200, 256, "gelu_tanh", g) < KTOL["bfloat16"]
+    assert tcgen05_wait_timeouts() == again

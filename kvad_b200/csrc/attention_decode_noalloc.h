@@ -16,6 +16,9 @@
 // The first call on a device looks up the array's device address (cudaGetSymbolAddress) with that
 // device current and keeps it; make that first call before any stream capture begins.  The call
 // itself allocates nothing: no cudaMalloc, no cudaFree, no library routine that allocates.
+// The address is kept in a plain per-device table without a lock: two host threads that make
+// their first call on one device at once both look it up and both store the same value, which
+// is harmless; no other state is shared between host threads.
 //
 // All calls share the one array, and it keeps what the last call left in it.  Nothing in it has to
 // start at zero - each call writes every word it later reads - but two calls that overlap on the

@@ -208,9 +208,19 @@ def test_greedy_generation_through_the_entry_point(engines, plains, model_dirs, 
             assert row.max() - row[tok] <= TOL[dtype] * np.abs(row).max() * 2, f"token {j} of prompt {len(p)}"
     if dtype == "float32":
         assert exact == 24
-    # batches one after another give the same tokens as all at once
+    # batches one after another give the same tokens as all at once.  In 32-bit that is exact (a row's bits do not
+    # depend on its company); in bfloat16 the residual products add their K splits with atomics, so logits can
+    # differ in the last bit between runs and a near tie may fall the other way: there the tokens must still be
+    # the oracle's best within the tolerance.
     again = e.generate(prompts, max_tokens=8, temperature=0.0, batch_size=2)
-    assert again == outs
+    if dtype == "float32":
+        assert again == outs
+    else:
+        for p, o in zip(prompts, again):
+            ref = oracle.logits(p + o)
+            for j, tok in enumerate(o):
+                row = ref[len(p) - 1 + j]
+                assert row.max() - row[tok] <= TOL[dtype] * np.abs(row).max() * 2, f"second run: token {j} of prompt {len(p)}"
 
 
 @pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16"), ("D", "bfloat16")])

@@ -13,6 +13,10 @@
 // few rows; in 32-bit this is the decode road of the float32 engine up to 16 rows (the tiled kernel
 // of linear_simt.cu would run one row in a 64-row tile), every product an fmaf into a 32-bit sum.
 //
+// Two columns a warp on their way at a time (twice the registers for weights) were tried and lost: fewer
+// warps fit an SM, and the warps in flight are what keeps memory busy (GPT-2 XL sizes, one row, an
+// 8-layer model: 2 776 against 3 220 tokens a second; 32-bit GPT-2 small: 2 900 against 3 300).
+//
 // Sums are 32-bit; the order of additions for an output depends on K only, so a row's bits do not
 // depend on its company.  (It is another order than the tiled kernel's: the two agree to rounding.)
 #include "common.cuh"
@@ -21,6 +25,12 @@ using namespace kvad;
 
 namespace {
 
+LookAhead g_ahead = {nullptr, 0};      // what the next launch also asks the L2 for (kvad_linear_rows_look_ahead)
+
+#ifndef KVAD_ROWS_TARGET_CTAS
+#define KVAD_ROWS_TARGET_CTAS 592      // CTAs a launch aims at, four an SM; one row, tokens a second at GPT-2 XL's sizes (8 layers) /
+                                       // GPT-2 small: 148 -> 2650 / 3447, 296 -> 3119 / 3744, 592 -> 3222 / 3943, 1184 -> 3115 / 3948
+#endif
 constexpr int ROWS_THREADS = 256;
 constexpr int ROWS_WARPS = ROWS_THREADS / 32;
 
@@ -55,7 +65,7 @@ template <typename T, int MR, int NI, int EPI>
 __global__ void __launch_bounds__(ROWS_THREADS)
 linear_rows_kernel(const T* __restrict__ A, int64_t lda, const T* __restrict__ W,
                    const void* __restrict__ bias, int bias_f32, void* __restrict__ out, int64_t ldo,
-                   int M, int N, int K, int cols_per_warp) {
+                   int M, int N, int K, int cols_per_warp, const LookAhead ahead) {
   constexpr int VE = Piece<T>::VE;
   extern __shared__ __align__(16) unsigned char rows_smem[];
   T* As = reinterpret_cast<T*>(rows_smem);      // [MR][K]
@@ -74,6 +84,7 @@ linear_rows_kernel(const T* __restrict__ A, int64_t lda, const T* __restrict__ W
   };
   fetch(col0);
   float b0 = (bias != nullptr && col0 < N) ? load_param(bias, col0, bias_f32) : 0.f;
+  l2_look_ahead(ahead, blockIdx.x, gridDim.x, threadIdx.x, ROWS_THREADS);
 
   pdl_wait();
   // the activation rows -> shared memory (rows past M are zero)
@@ -139,8 +150,8 @@ linear_rows_kernel(const T* __restrict__ A, int64_t lda, const T* __restrict__ W
 template <typename T, int MR, int NI>
 int launch_epi(int epilogue, const void* A, int64_t lda, const void* W, const void* bias, int bias_f32, void* out,
                int64_t ldo, int M, int N, int K, cudaStream_t stream) {
-  // columns per warp: enough CTAs to cover the SMs twice, not more
-  int cpw = (N + ROWS_WARPS * 296 - 1) / (ROWS_WARPS * 296);
+  // columns per warp: enough CTAs to fill every SM with four, not more
+  int cpw = (N + ROWS_WARPS * KVAD_ROWS_TARGET_CTAS - 1) / (ROWS_WARPS * KVAD_ROWS_TARGET_CTAS);
   if (cpw < 1) cpw = 1;
   const int grid = (N + ROWS_WARPS * cpw - 1) / (ROWS_WARPS * cpw);
   const size_t smem = (size_t)MR * K * sizeof(T);
@@ -155,7 +166,7 @@ int launch_epi(int epilogue, const void* A, int64_t lda, const void* W, const vo
       configured = smem;                                                                                            \
     }                                                                                                               \
     kvad_launch(linear_rows_kernel<T, MR, NI, E>, dim3(grid), dim3(ROWS_THREADS), smem, stream, (const T*)A,        \
-                lda, (const T*)W, bias, bias_f32, out, ldo, M, N, K, cpw);                                          \
+                lda, (const T*)W, bias, bias_f32, out, ldo, M, N, K, cpw, g_ahead);                                 \
   }
   switch (epilogue) {
     case EPI_STORE: KVAD_ROWS(EPI_STORE) break;
@@ -192,19 +203,26 @@ int launch_rows(int epilogue, const void* A, int64_t lda, const void* W, const v
 
 }  // namespace
 
-// Refuses (KVAD_ERR_UNSUPPORTED) more than 16 rows, K beyond 4096 or not a multiple of 8 (bfloat16) / 4 (float32),
+// Refuses (KVAD_ERR_UNSUPPORTED) more than 16 rows, K beyond 1024 16-byte pieces (8192 in bfloat16, 4096 in
+// float32: 32 pieces a lane) or not a multiple of a piece,
 // or operands that are not 16-byte aligned; the caller then takes another kernel.
 KVAD_EXPORT int kvad_linear_rows(int dtype, const void* A, int64_t lda, const void* W, const void* bias, int bias_f32, void* out,
                                  int64_t ldo, int M, int N, int K, int epilogue, cudaStream_t stream) {
   KVAD_REQUIRE(M >= 0 && N > 0 && K > 0, "linear_rows: bad sizes M=%d N=%d K=%d", M, N, K);
   if (dtype != KVAD_DTYPE_BF16 && dtype != KVAD_DTYPE_F32) KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "linear_rows: unknown dtype %d", dtype);
   const int ve = dtype == KVAD_DTYPE_BF16 ? 8 : 4;
-  if (M > 16 || K > 4096 || K % ve != 0 || lda % ve != 0 || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
-    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "linear_rows: takes at most 16 rows, K a multiple of %d up to 4096 and 16-byte aligned operands (M=%d K=%d)", ve, M, K);
+  if (M > 16 || K > 1024 * ve || K % ve != 0 || lda % ve != 0 || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
+    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "linear_rows: takes at most 16 rows, K a multiple of %d up to %d and 16-byte aligned operands (M=%d K=%d)", ve, 1024 * ve, M, K);
   KVAD_REQUIRE(lda >= K && ldo >= N, "linear_rows: leading dimensions lda=%lld ldo=%lld too small", (long long)lda, (long long)ldo);
   if (M == 0) return KVAD_OK;
-  if (dtype == KVAD_DTYPE_BF16) return launch_rows<__nv_bfloat16>(epilogue, A, lda, W, bias, bias_f32, out, ldo, M, N, K, stream);
-  return launch_rows<float>(epilogue, A, lda, W, bias, bias_f32, out, ldo, M, N, K, stream);
+  const int rc = dtype == KVAD_DTYPE_BF16 ? launch_rows<__nv_bfloat16>(epilogue, A, lda, W, bias, bias_f32, out, ldo, M, N, K, stream)
+                                          : launch_rows<float>(epilogue, A, lda, W, bias, bias_f32, out, ldo, M, N, K, stream);
+  g_ahead = {nullptr, 0};
+  return rc;
 }
+
+// The NEXT launch of kvad_linear_rows also asks the L2 for these bytes (the weights of the product after it);
+// they must stay mapped while that launch may run, captured graphs included.  One launch uses the hint up.
+KVAD_EXPORT void kvad_linear_rows_look_ahead(const void* ptr, int64_t bytes) { g_ahead = {ptr, (long long)bytes}; }
 
 KVAD_DEFINE_LAST_ERROR()

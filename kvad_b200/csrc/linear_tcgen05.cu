@@ -54,6 +54,7 @@ constexpr int SMEM_BUDGET_WIDE = 192 * 1024;     // the wide form keeps 33 KB fo
 
 bool g_no_3d = false;               // tests: keep the swapped form on one TMA load per K block
 bool g_test_skip_load = false;      // tests: the next launch of the swapped form (one load per K block) leaves out its first load
+LookAhead g_ahead = {nullptr, 0};   // what the next launch also asks the L2 for (kvad_linear_tcgen05_look_ahead)
 bool g_no_cluster_k = false;        // tests: never split K over a cluster under a storing epilogue
 bool g_no_tma_out = false;          // tests: the wide form writes its output with plain stores
 bool g_force_3d = false;            // tests: take the grouped three-dimensional loads at every row count
@@ -149,7 +150,7 @@ __global__ void __launch_bounds__(NUM_THREADS_WIDE, 1)
 linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                       const __grid_constant__ CUtensorMap map_out, int tma_out,
                       const void* __restrict__ bias, int bias_f32, void* __restrict__ out, int64_t ldo,
-                      int M, int N, int K, int kb_per_split, int n_splits) {
+                      int M, int N, int K, int kb_per_split, int n_splits, const LookAhead ahead) {
   using T = Tile<BN>;
   constexpr int STAGES = T::STAGES, ACC_BUFS = T::ACC_BUFS;
   extern __shared__ uint8_t smem_raw[];
@@ -286,6 +287,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         asm volatile("bar.sync 1, 256;" ::: "memory");     // the eight epilogue warps
       }
       if (!waited) {
+        l2_look_ahead(ahead, blockIdx.x, gridDim.x, threadIdx.x - 64, NUM_THREADS_WIDE - 64);
         pdl_wait();
         waited = true;
       }
@@ -402,7 +404,7 @@ template <int MB, int EPI, int TM>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 linear_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                              const void* __restrict__ bias, int bias_flags, void* __restrict__ out, int64_t ldo,
-                             int M, int N, int K, int kb_per_split) {
+                             int M, int N, int K, int kb_per_split, const LookAhead ahead) {
   using T = SkinnyTile<MB, TM>;
   constexpr int STAGES = T::STAGES;
   const int bias_f32 = bias_flags & 1;
@@ -486,6 +488,7 @@ linear_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __
     const int n = has_row ? n0 + (TM == 128 ? quarter * 32 + lane : quarter * 16 + lane) : N;
     float b = 0.f;                                   // a parameter: fetched while the product is still running
     if (blockIdx.y == 0 && bias != nullptr && n < N) b = load_param(bias, n, bias_f32);
+    l2_look_ahead(ahead, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y, threadIdx.x - 64, NUM_THREADS - 64);
     pdl_wait();
     const bool ok = mbar_wait(tmem_full_bar, 0);
     tc_fence_after();
@@ -542,7 +545,7 @@ template <int MB, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 linear_tcgen05_skinny3d_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                                const void* __restrict__ bias, int bias_f32, void* __restrict__ out, int64_t ldo,
-                               int M, int N, int K, int kb_per_split, int stages, int cluster_reduce) {
+                               int M, int N, int K, int kb_per_split, int stages, int cluster_reduce, const LookAhead ahead) {
   constexpr uint32_t W_BYTES = BM * BK * 2;            // one K block of 128 weight rows
   constexpr uint32_t A_BYTES = MB * BK * 2;            // one K block of the activation rows
   constexpr int TMEM_COLS = MB < 32 ? 32 : MB;
@@ -644,6 +647,7 @@ linear_tcgen05_skinny3d_kernel(const __grid_constant__ CUtensorMap map_a, const 
     float b = 0.f;
     if ((blockIdx.y == 0 || cluster_reduce) && bias != nullptr && n < N) b = load_param(bias, n, bias_f32);
     if (cluster_reduce) cluster_arrive();
+    l2_look_ahead(ahead, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y, threadIdx.x - 64, NUM_THREADS - 64);
     pdl_wait();
     const bool ok = mbar_wait(tmem_full_bar, 0);
     tc_fence_after();
@@ -869,7 +873,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, const void* bias, int b
   KVAD_REQUIRE(n_tiles < (1ll << 30), "linear_tcgen05: %lld tiles are more than one launch takes", (long long)n_tiles);
   const int ctas = n_tiles < sm_count() ? (int)n_tiles : sm_count();      // one CTA per SM walks the tiles
   kvad_launch(linear_tcgen05_kernel<BN, EPI>, dim3(ctas), dim3(NUM_THREADS_WIDE), T::SMEM, stream, ma, mw, mo, tma_out, bias,
-              bias_f32, out, ldo, M, N, K, kb_per_split, z);
+              bias_f32, out, ldo, M, N, K, kb_per_split, z, g_ahead);
   KVAD_CHECK_LAUNCH("linear_tcgen05");
   return KVAD_OK;
 }
@@ -903,7 +907,7 @@ int launch_skinny(const CUtensorMap& ma, const CUtensorMap& mw, const void* bias
   dim3 grid((N + TM - 1) / TM, z);
   const int test_skip = g_test_skip_load ? 2 : 0;       // rides in a free bit of bias_f32
   g_test_skip_load = false;
-  kvad_launch(linear_tcgen05_skinny_kernel<MB, EPI, TM>, grid, dim3(NUM_THREADS), T::SMEM, stream, ma, mw, bias, bias_f32 | test_skip, out, ldo, M, N, K, kb_per_split);
+  kvad_launch(linear_tcgen05_skinny_kernel<MB, EPI, TM>, grid, dim3(NUM_THREADS), T::SMEM, stream, ma, mw, bias, bias_f32 | test_skip, out, ldo, M, N, K, kb_per_split, g_ahead);
   KVAD_CHECK_LAUNCH("linear_tcgen05_skinny");
   return KVAD_OK;
 }
@@ -934,10 +938,10 @@ int launch_skinny3d(const CUtensorMap& ma, const CUtensorMap& mw, const void* bi
   }
   if (cluster_reduce)
     kvad_launch_cluster(linear_tcgen05_skinny3d_kernel<MB, EPI>, dim3((N + BM - 1) / BM, z), dim3(NUM_THREADS), smem, stream,
-                        dim3(1, z, 1), ma, mw, bias, bias_f32, out, ldo, M, N, K, kb_per_split, stages, 1);
+                        dim3(1, z, 1), ma, mw, bias, bias_f32, out, ldo, M, N, K, kb_per_split, stages, 1, g_ahead);
   else
     kvad_launch(linear_tcgen05_skinny3d_kernel<MB, EPI>, dim3((N + BM - 1) / BM, z), dim3(NUM_THREADS), smem, stream, ma, mw,
-                bias, bias_f32, out, ldo, M, N, K, kb_per_split, stages, 0);
+                bias, bias_f32, out, ldo, M, N, K, kb_per_split, stages, 0, g_ahead);
   KVAD_CHECK_LAUNCH("linear_tcgen05_skinny3d");
   return KVAD_OK;
 }
@@ -961,9 +965,9 @@ int launch_skinny3d_epi(int epilogue, const CUtensorMap& ma, const CUtensorMap& 
 // form (16, 32, 64, 128, 192 or 256); bits 16-23 how many CTAs share K (residual epilogue only);
 // bits 24-25 the form: 1 wide (activation rows on the M side), 2 swapped (at most 64 rows; the
 // tile width then means weight rows per CTA, 64 or 128).
-KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, const void* bias, int bias_f32,
-                                    void* out, int64_t ldo, int M, int N, int K, int epilogue, int force,
-                                    cudaStream_t stream) {
+static int linear_tcgen05_launch(const void* A, int64_t lda, const void* W, const void* bias, int bias_f32,
+                                 void* out, int64_t ldo, int M, int N, int K, int epilogue, int force,
+                                 cudaStream_t stream) {
   KVAD_REQUIRE(M >= 0 && N > 0 && K > 0, "linear_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
   if (K % 8 != 0 || lda % 8 != 0)
     KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "linear_tcgen05: K=%d and the row stride %lld must be multiples of 8 (TMA strides are multiples of 16 bytes)", K, (long long)lda);
@@ -1107,6 +1111,18 @@ KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, c
     default: return launch_epi<256>(epilogue, ma, mw, bias, bias_f32, out, ldo, M, N, K, splits, stream);
   }
 }
+
+KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, const void* bias, int bias_f32,
+                                    void* out, int64_t ldo, int M, int N, int K, int epilogue, int force,
+                                    cudaStream_t stream) {
+  const int rc = linear_tcgen05_launch(A, lda, W, bias, bias_f32, out, ldo, M, N, K, epilogue, force, stream);
+  g_ahead = {nullptr, 0};
+  return rc;
+}
+
+// The NEXT launch of kvad_linear_tcgen05 also asks the L2 for these bytes (the weights of the product after it);
+// they must stay mapped while that launch may run, captured graphs included.  One launch uses the hint up.
+KVAD_EXPORT void kvad_linear_tcgen05_look_ahead(const void* ptr, int64_t bytes) { g_ahead = {ptr, (long long)bytes}; }
 
 // Tests: 1 keeps the swapped form on two-dimensional loads (one per K block) for every K; 2 takes the
 // grouped three-dimensional loads whenever K allows; 0 is the kernel's own choice (them, up to 16 rows).

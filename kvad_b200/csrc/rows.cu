@@ -125,66 +125,90 @@ __device__ __forceinline__ void load_params8(const void* p, int k0, int is_f32, 
   }
 }
 
-// The same for narrow rows: one warp per row, the row in registers (NI chunks of 8 per
-// lane, so widths up to NI * 256), sums met by shuffles only.  Gain and bias are parameters, not the
-// previous kernel's work: they are fetched before the dependent-launch wait.
-template <typename T, int NI>
+// The same with the row in registers: WPR warps per row (1: widths up to NI * 256, sums met by shuffles only;
+// 4: a block of four warps per row, widths up to NI * 1024, the warps' sums added in warp order through
+// shared memory), NI chunks of 8 per thread.  Gain and bias are parameters, not the previous kernel's
+// work: they are fetched before the dependent-launch wait.
+template <typename T, int NI, int WPR>
 __global__ void __launch_bounds__(128)
 layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
                       const void* __restrict__ gain, const void* __restrict__ bias, int params_f32,
                       T* __restrict__ out, int n_rows, int width, float eps) {
+  constexpr int TPR = 32 * WPR;                     // threads per row
+  __shared__ float met[2][4];
   pdl_launch_dependents();
-  const int lane = threadIdx.x & 31;
-  const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int t = threadIdx.x % TPR, warp = threadIdx.x >> 5;
+  const int r = blockIdx.x * (4 / WPR) + threadIdx.x / TPR;
   float g[NI][8], b[NI][8];
 #pragma unroll
   for (int i = 0; i < NI; ++i) {
-    const int k0 = (lane + 32 * i) * 8;
+    const int k0 = (t + TPR * i) * 8;
     load_params8(gain, k0, params_f32, k0 < width, g[i]);
     load_params8(bias, k0, params_f32, k0 < width && bias != nullptr, b[i]);
   }
   pdl_wait();
-  if (r >= n_rows) return;
+  if (r >= n_rows) return;                          // (with four warps per row the whole block leaves)
   const float* xr = x + (int64_t)(row_index ? row_index[r] : r) * width;
   float v[NI][8];
   float sum = 0.f;
 #pragma unroll
   for (int i = 0; i < NI; ++i) {
-    const int k0 = (lane + 32 * i) * 8;
+    const int k0 = (t + TPR * i) * 8;
     if (k0 < width) {
       const float4 a = *reinterpret_cast<const float4*>(xr + k0), c = *reinterpret_cast<const float4*>(xr + k0 + 4);
       v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w; v[i][4] = c.x; v[i][5] = c.y; v[i][6] = c.z; v[i][7] = c.w;
     } else {
 #pragma unroll
-      for (int t = 0; t < 8; ++t) v[i][t] = 0.f;
+      for (int u = 0; u < 8; ++u) v[i][u] = 0.f;
     }
 #pragma unroll
-    for (int t = 0; t < 8; ++t) sum += v[i][t];
+    for (int u = 0; u < 8; ++u) sum += v[i][u];
   }
-  const float mean = warp_sum(sum) / (float)width;
+  sum = warp_sum(sum);
+  if (WPR == 4) {
+    if ((threadIdx.x & 31) == 0) met[0][warp] = sum;
+    __syncthreads();
+    sum = ((met[0][0] + met[0][1]) + met[0][2]) + met[0][3];
+  }
+  const float mean = sum / (float)width;
   float sq = 0.f;
 #pragma unroll
   for (int i = 0; i < NI; ++i) {
-    if ((lane + 32 * i) * 8 < width) {
+    if ((t + TPR * i) * 8 < width) {
 #pragma unroll
-      for (int t = 0; t < 8; ++t) {
-        const float d = v[i][t] - mean;
+      for (int u = 0; u < 8; ++u) {
+        const float d = v[i][u] - mean;
         sq = fmaf(d, d, sq);
       }
     }
   }
-  const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
+  sq = warp_sum(sq);
+  if (WPR == 4) {
+    if ((threadIdx.x & 31) == 0) met[1][warp] = sq;
+    __syncthreads();
+    sq = ((met[1][0] + met[1][1]) + met[1][2]) + met[1][3];
+  }
+  const float inv = 1.0f / sqrtf(sq / (float)width + eps);
   T* o = out + (int64_t)r * width;
 #pragma unroll
   for (int i = 0; i < NI; ++i) {
-    const int k0 = (lane + 32 * i) * 8;
+    const int k0 = (t + TPR * i) * 8;
     if (k0 < width) {
       float y[8];
 #pragma unroll
-      for (int t = 0; t < 8; ++t) y[t] = (v[i][t] - mean) * inv * g[i][t] + b[i][t];
+      for (int u = 0; u < 8; ++u) y[u] = (v[i][u] - mean) * inv * g[i][u] + b[i][u];
       store8(o + k0, y);
     }
   }
+}
+
+template <typename T>
+void launch_layernorm_regs(const float* x, const int* row_index, const void* gain, const void* bias, int params_f32, T* out,
+                           int n_rows, int width, float eps, cudaStream_t stream) {
+  if (width <= 1024)       // narrow rows: a warp per row
+    kvad_launch(layernorm_warp_kernel<T, 4, 1>, dim3((n_rows + 3) / 4), dim3(128), 0, stream, x, row_index, gain, bias, params_f32, out, n_rows, width, eps);
+  else                     // up to 4096: four warps per row
+    kvad_launch(layernorm_warp_kernel<T, 4, 4>, dim3(n_rows), dim3(128), 0, stream, x, row_index, gain, bias, params_f32, out, n_rows, width, eps);
 }
 
 KVAD_EXPORT int kvad_layernorm(int out_dtype, const float* x, const int* row_index, const void* gain,
@@ -193,15 +217,14 @@ KVAD_EXPORT int kvad_layernorm(int out_dtype, const float* x, const int* row_ind
   KVAD_REQUIRE(n_rows >= 0 && width > 0, "layernorm: bad sizes rows=%d width=%d", n_rows, width);
   KVAD_REQUIRE(gain != nullptr, "layernorm: no gain");
   if (n_rows == 0) return KVAD_OK;
-  if (width % 8 == 0 && width <= 1024 &&
+  if (width % 8 == 0 && width <= 4096 &&
       ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(gain) | reinterpret_cast<uintptr_t>(bias) |
         reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
-    // narrow rows: a warp per row
-    const dim3 grid((n_rows + 3) / 4), block(128);
+    // the row in registers
     if (out_dtype == KVAD_DTYPE_F32)
-      kvad_launch(layernorm_warp_kernel<float, 4>, grid, block, 0, stream, x, row_index, gain, bias, params_f32, (float*)out, n_rows, width, eps);
+      launch_layernorm_regs<float>(x, row_index, gain, bias, params_f32, (float*)out, n_rows, width, eps, stream);
     else if (out_dtype == KVAD_DTYPE_BF16)
-      kvad_launch(layernorm_warp_kernel<__nv_bfloat16, 4>, grid, block, 0, stream, x, row_index, gain, bias, params_f32, (__nv_bfloat16*)out, n_rows, width, eps);
+      launch_layernorm_regs<__nv_bfloat16>(x, row_index, gain, bias, params_f32, (__nv_bfloat16*)out, n_rows, width, eps, stream);
     else
       KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "layernorm: unknown dtype %d", out_dtype);
     KVAD_CHECK_LAUNCH("layernorm");

@@ -53,10 +53,12 @@ _SIGNATURES = {
         "kvad_linear_tcgen05": [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int,
                                 c_int, c_int, c_void_p],
         "kvad_linear_tcgen05_status": [],
+        "kvad_linear_tcgen05_look_ahead": [c_void_p, c_int64],
     },
     "linear_rows": {
         "kvad_linear_rows": [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int,
                              c_void_p],
+        "kvad_linear_rows_look_ahead": [c_void_p, c_int64],
     },
     "attention_simt": {
         "kvad_attention_simt": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
@@ -221,6 +223,13 @@ class Ops:
         self.rows_linear_max = (2 if dtype == torch.bfloat16 else 16) if "linear_rows" in build.sources() else 0
         self._counters = None       # zeroed ints the decode kernel counts finished splits in (left zeroed by it)
         from . import profile
+        # Looking ahead: a product's kernel also asks the L2 for the weights of the product that FOLLOWED it the
+        # last time round (the order of a model's products repeats step after step, so it is learned, not
+        # declared), at most LOOK_AHEAD_BYTES of them.  Memory then streams through the dependent chains of
+        # the kernels in between.  KVAD_LOOK_AHEAD=0 switches it off.
+        self.look_ahead = os.environ.get("KVAD_LOOK_AHEAD", "1") != "0"
+        self._followed_by: dict[int, torch.Tensor] = {}
+        self._last_weight: Optional[torch.Tensor] = None
         if profile.enabled():       # KVAD_PROFILE=1: a table of device time per operation at exit
             profile.instrument(self)
 
@@ -228,7 +237,19 @@ class Ops:
         """Everything on the host that decides which kernels a step of a given shape launches; part of
         the key under which a step's CUDA graph is kept."""
         return (_switch_epoch, self.tensor_core_linear, self.tensor_core_prefill, self.fast_decode,
-                self.rows_linear_max)
+                self.rows_linear_max, self.look_ahead)
+
+    LOOK_AHEAD_BYTES = 48 << 20
+
+    def _next_weights(self, weight) -> Optional[torch.Tensor]:
+        """Notes that `weight` follows the weight of the product before, and says what followed `weight` last time."""
+        if not self.look_ahead:
+            return None
+        last, self._last_weight = self._last_weight, weight
+        if last is not None and last is not weight:
+            self._followed_by[last.data_ptr()] = weight
+        nxt = self._followed_by.get(weight.data_ptr())
+        return nxt if nxt is not None and nxt.is_cuda else None
 
     # -- embedding -----------------------------------------------------------------
     def embed(self, tokens, positions, wte, wpe, out) -> None:
@@ -296,17 +317,25 @@ class Ops:
                 raise KernelError(f"linear: bias must be float32 or bfloat16, not {bias.dtype}")
         ve = 8 if self.dtype == torch.bfloat16 else 4          # elements of a 16-byte piece
         rows_out_ok = self.dtype == torch.float32 or n <= self.ROWS_LINEAR_MAX_OUT
-        if ((form == "rows" or (form == "auto" and m <= self.rows_linear_max and rows_out_ok)) and m <= 16 and k <= 4096
+        # (by itself only up to K = 4096: beyond, one column a warp is too long a chain - measured at 1600 x 6400,
+        # one row: the tensor-core form with K split over twelve CTAs is 10 % faster on the step)
+        if ((form == "rows" or (form == "auto" and m <= self.rows_linear_max and rows_out_ok and k <= 4096)) and m <= 16 and k <= 1024 * ve
                 and k % ve == 0 and lda % ve == 0 and (1 << max(0, m - 1).bit_length()) * k * a.element_size() <= 200 * 1024
                 and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and "linear_rows" in build.sources()):
             h = lib("linear_rows")
+            ahead = self._next_weights(weight)
+            if ahead is not None:
+                h.kvad_linear_rows_look_ahead(_ptr(ahead), min(ahead.numel() * ahead.element_size(), self.LOOK_AHEAD_BYTES))
             _check(h.kvad_linear_rows(self.code, _ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k, epi,
                                       _stream()), h)
             return
         if form == "rows":
-            raise KernelError("linear: the weight-streaming form takes at most 16 rows and K a multiple of a 16-byte piece up to 4096")
+            raise KernelError("linear: the weight-streaming form takes at most 16 rows and K a multiple of a 16-byte piece, at most 1024 pieces")
         if self.tensor_core_linear and tcgen05_takes(a, weight, out, lda, ldo):
             h = lib("linear_tcgen05")
+            ahead = self._next_weights(weight)
+            if ahead is not None:
+                h.kvad_linear_tcgen05_look_ahead(_ptr(ahead), min(ahead.numel() * ahead.element_size(), self.LOOK_AHEAD_BYTES))
             _check(h.kvad_linear_tcgen05(_ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k,
                                          epi, (int(tile) & 0xffff) | ((int(splits) & 0xff) << 16)
                                          | ({"auto": 0, "wide": 1, "swapped": 2}.get(form, 0) << 24), _stream()), h)

@@ -150,25 +150,6 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
   return __float2bfloat16_rn(v);
 }
 
-// Asks the L2 for [p, p + bytes) - what a LATER kernel of the stream will read, in practice the next
-// product's weights - a 128-byte line per instruction, the lines shared out over the grid's CTAs and the
-// given threads of each.  Nothing waits for it and nothing depends on it: while this kernel and the ones
-// after it go through their dependent chains, memory keeps streaming, and the next product finds its
-// weights in the L2 instead of fetching them after its wait.  The bytes must be mapped (weights are).
-struct LookAhead {
-  const void* ptr;
-  long long bytes;
-};
-__device__ __forceinline__ void l2_look_ahead(const LookAhead& la, int cta, int n_ctas, int thread, int n_threads) {
-  if (la.ptr == nullptr || la.bytes <= 0) return;
-  const long long lines = (la.bytes + 127) >> 7;
-  const long long per = (lines + n_ctas - 1) / n_ctas;
-  const long long begin = (long long)cta * per;
-  const long long end = begin + per < lines ? begin + per : lines;
-  const char* base = reinterpret_cast<const char*>(la.ptr);
-  for (long long i = begin + thread; i < end; i += n_threads) asm volatile("prefetch.global.L2 [%0];" ::"l"(base + (i << 7)));
-}
-
 // A parameter vector (bias, gain) may be stored in 32-bit even when the
 // activations are bfloat16: `is_f32` says which.
 __device__ __forceinline__ float load_param(const void* p, int64_t i, int is_f32) {

@@ -25,8 +25,6 @@ using namespace kvad;
 
 namespace {
 
-LookAhead g_ahead = {nullptr, 0};      // what the next launch also asks the L2 for (kvad_linear_rows_look_ahead)
-
 #ifndef KVAD_ROWS_TARGET_CTAS
 #define KVAD_ROWS_TARGET_CTAS 592      // CTAs a launch aims at, four an SM; one row, tokens a second at GPT-2 XL's sizes (8 layers) /
                                        // GPT-2 small: 148 -> 2650 / 3447, 296 -> 3119 / 3744, 592 -> 3222 / 3943, 1184 -> 3115 / 3948
@@ -65,7 +63,7 @@ template <typename T, int MR, int NI, int EPI>
 __global__ void __launch_bounds__(ROWS_THREADS)
 linear_rows_kernel(const T* __restrict__ A, int64_t lda, const T* __restrict__ W,
                    const void* __restrict__ bias, int bias_f32, void* __restrict__ out, int64_t ldo,
-                   int M, int N, int K, int cols_per_warp, const LookAhead ahead) {
+                   int M, int N, int K, int cols_per_warp) {
   constexpr int VE = Piece<T>::VE;
   extern __shared__ __align__(16) unsigned char rows_smem[];
   T* As = reinterpret_cast<T*>(rows_smem);      // [MR][K]
@@ -84,7 +82,6 @@ linear_rows_kernel(const T* __restrict__ A, int64_t lda, const T* __restrict__ W
   };
   fetch(col0);
   float b0 = (bias != nullptr && col0 < N) ? load_param(bias, col0, bias_f32) : 0.f;
-  l2_look_ahead(ahead, blockIdx.x, gridDim.x, threadIdx.x, ROWS_THREADS);
 
   pdl_wait();
   // the activation rows -> shared memory (rows past M are zero)
@@ -166,7 +163,7 @@ int launch_epi(int epilogue, const void* A, int64_t lda, const void* W, const vo
       configured = smem;                                                                                            \
     }                                                                                                               \
     kvad_launch(linear_rows_kernel<T, MR, NI, E>, dim3(grid), dim3(ROWS_THREADS), smem, stream, (const T*)A,        \
-                lda, (const T*)W, bias, bias_f32, out, ldo, M, N, K, cpw, g_ahead);                                 \
+                lda, (const T*)W, bias, bias_f32, out, ldo, M, N, K, cpw);                                          \
   }
   switch (epilogue) {
     case EPI_STORE: KVAD_ROWS(EPI_STORE) break;
@@ -215,14 +212,8 @@ KVAD_EXPORT int kvad_linear_rows(int dtype, const void* A, int64_t lda, const vo
     KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "linear_rows: takes at most 16 rows, K a multiple of %d up to %d and 16-byte aligned operands (M=%d K=%d)", ve, 1024 * ve, M, K);
   KVAD_REQUIRE(lda >= K && ldo >= N, "linear_rows: leading dimensions lda=%lld ldo=%lld too small", (long long)lda, (long long)ldo);
   if (M == 0) return KVAD_OK;
-  const int rc = dtype == KVAD_DTYPE_BF16 ? launch_rows<__nv_bfloat16>(epilogue, A, lda, W, bias, bias_f32, out, ldo, M, N, K, stream)
-                                          : launch_rows<float>(epilogue, A, lda, W, bias, bias_f32, out, ldo, M, N, K, stream);
-  g_ahead = {nullptr, 0};
-  return rc;
+  if (dtype == KVAD_DTYPE_BF16) return launch_rows<__nv_bfloat16>(epilogue, A, lda, W, bias, bias_f32, out, ldo, M, N, K, stream);
+  return launch_rows<float>(epilogue, A, lda, W, bias, bias_f32, out, ldo, M, N, K, stream);
 }
-
-// The NEXT launch of kvad_linear_rows also asks the L2 for these bytes (the weights of the product after it);
-// they must stay mapped while that launch may run, captured graphs included.  One launch uses the hint up.
-KVAD_EXPORT void kvad_linear_rows_look_ahead(const void* ptr, int64_t bytes) { g_ahead = {ptr, (long long)bytes}; }
 
 KVAD_DEFINE_LAST_ERROR()

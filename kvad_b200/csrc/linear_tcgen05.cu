@@ -54,7 +54,6 @@ constexpr int SMEM_BUDGET_WIDE = 192 * 1024;     // the wide form keeps 33 KB fo
 
 bool g_no_3d = false;               // tests: keep the swapped form on one TMA load per K block
 bool g_test_skip_load = false;      // tests: the next launch of the swapped form (one load per K block) leaves out its first load
-LookAhead g_ahead = {nullptr, 0};   // what the next launch also asks the L2 for (kvad_linear_tcgen05_look_ahead)
 bool g_no_cluster_k = false;        // tests: never split K over a cluster under a storing epilogue
 bool g_no_tma_out = false;          // tests: the wide form writes its output with plain stores
 bool g_force_3d = false;            // tests: take the grouped three-dimensional loads at every row count
@@ -150,7 +149,7 @@ __global__ void __launch_bounds__(NUM_THREADS_WIDE, 1)
 linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                       const __grid_constant__ CUtensorMap map_out, int tma_out,
                       const void* __restrict__ bias, int bias_f32, void* __restrict__ out, int64_t ldo,
-                      int M, int N, int K, int kb_per_split, int n_splits, const LookAhead ahead) {
+                      int M, int N, int K, int kb_per_split, int n_splits) {
   using T = Tile<BN>;
   constexpr int STAGES = T::STAGES, ACC_BUFS = T::ACC_BUFS;
   extern __shared__ uint8_t smem_raw[];
@@ -287,7 +286,6 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         asm volatile("bar.sync 1, 256;" ::: "memory");     // the eight epilogue warps
       }
       if (!waited) {
-        l2_look_ahead(ahead, blockIdx.x, gridDim.x, threadIdx.x - 64, NUM_THREADS_WIDE - 64);
         pdl_wait();
         waited = true;
       }
@@ -404,7 +402,7 @@ template <int MB, int EPI, int TM>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 linear_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                              const void* __restrict__ bias, int bias_flags, void* __restrict__ out, int64_t ldo,
-                             int M, int N, int K, int kb_per_split, const LookAhead ahead) {
+                             int M, int N, int K, int kb_per_split) {
   using T = SkinnyTile<MB, TM>;
   constexpr int STAGES = T::STAGES;
   const int bias_f32 = bias_flags & 1;
@@ -488,7 +486,6 @@ linear_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __
     const int n = has_row ? n0 + (TM == 128 ? quarter * 32 + lane : quarter * 16 + lane) : N;
     float b = 0.f;                                   // a parameter: fetched while the product is still running
     if (blockIdx.y == 0 && bias != nullptr && n < N) b = load_param(bias, n, bias_f32);
-    l2_look_ahead(ahead, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y, threadIdx.x - 64, NUM_THREADS - 64);
     pdl_wait();
     const bool ok = mbar_wait(tmem_full_bar, 0);
     tc_fence_after();
@@ -540,12 +537,15 @@ linear_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __
 // K blocks of 128 weight rows (64 KB for G = 4); a CTA of the qkv product issues 4 loads instead of 24.
 // ---------------------------------------------------------------------------------------------
 constexpr int W_GROUP = 4;          // K blocks of weights per TMA instruction and pipeline stage
+#ifndef KVAD_MAX_SPLIT_CTAS
+#define KVAD_MAX_SPLIT_CTAS 444     // CTAs of a launch whose K is split: three an SM
+#endif
 
 template <int MB, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 linear_tcgen05_skinny3d_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                                const void* __restrict__ bias, int bias_f32, void* __restrict__ out, int64_t ldo,
-                               int M, int N, int K, int kb_per_split, int stages, int cluster_reduce, const LookAhead ahead) {
+                               int M, int N, int K, int kb_per_split, int stages, int cluster_reduce) {
   constexpr uint32_t W_BYTES = BM * BK * 2;            // one K block of 128 weight rows
   constexpr uint32_t A_BYTES = MB * BK * 2;            // one K block of the activation rows
   constexpr int TMEM_COLS = MB < 32 ? 32 : MB;
@@ -574,7 +574,6 @@ linear_tcgen05_skinny3d_kernel(const __grid_constant__ CUtensorMap map_a, const 
   const int kb_end = kb_begin + kb_per_split < kb_total ? kb_begin + kb_per_split : kb_total;
   const int num_kb = kb_end - kb_begin;
   const int n_groups = (num_kb + W_GROUP - 1) / W_GROUP;
-
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(&w_full[s], 1);
@@ -647,7 +646,6 @@ linear_tcgen05_skinny3d_kernel(const __grid_constant__ CUtensorMap map_a, const 
     float b = 0.f;
     if ((blockIdx.y == 0 || cluster_reduce) && bias != nullptr && n < N) b = load_param(bias, n, bias_f32);
     if (cluster_reduce) cluster_arrive();
-    l2_look_ahead(ahead, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y, threadIdx.x - 64, NUM_THREADS - 64);
     pdl_wait();
     const bool ok = mbar_wait(tmem_full_bar, 0);
     tc_fence_after();
@@ -873,7 +871,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, const void* bias, int b
   KVAD_REQUIRE(n_tiles < (1ll << 30), "linear_tcgen05: %lld tiles are more than one launch takes", (long long)n_tiles);
   const int ctas = n_tiles < sm_count() ? (int)n_tiles : sm_count();      // one CTA per SM walks the tiles
   kvad_launch(linear_tcgen05_kernel<BN, EPI>, dim3(ctas), dim3(NUM_THREADS_WIDE), T::SMEM, stream, ma, mw, mo, tma_out, bias,
-              bias_f32, out, ldo, M, N, K, kb_per_split, z, g_ahead);
+              bias_f32, out, ldo, M, N, K, kb_per_split, z);
   KVAD_CHECK_LAUNCH("linear_tcgen05");
   return KVAD_OK;
 }
@@ -907,7 +905,7 @@ int launch_skinny(const CUtensorMap& ma, const CUtensorMap& mw, const void* bias
   dim3 grid((N + TM - 1) / TM, z);
   const int test_skip = g_test_skip_load ? 2 : 0;       // rides in a free bit of bias_f32
   g_test_skip_load = false;
-  kvad_launch(linear_tcgen05_skinny_kernel<MB, EPI, TM>, grid, dim3(NUM_THREADS), T::SMEM, stream, ma, mw, bias, bias_f32 | test_skip, out, ldo, M, N, K, kb_per_split, g_ahead);
+  kvad_launch(linear_tcgen05_skinny_kernel<MB, EPI, TM>, grid, dim3(NUM_THREADS), T::SMEM, stream, ma, mw, bias, bias_f32 | test_skip, out, ldo, M, N, K, kb_per_split);
   KVAD_CHECK_LAUNCH("linear_tcgen05_skinny");
   return KVAD_OK;
 }
@@ -938,10 +936,10 @@ int launch_skinny3d(const CUtensorMap& ma, const CUtensorMap& mw, const void* bi
   }
   if (cluster_reduce)
     kvad_launch_cluster(linear_tcgen05_skinny3d_kernel<MB, EPI>, dim3((N + BM - 1) / BM, z), dim3(NUM_THREADS), smem, stream,
-                        dim3(1, z, 1), ma, mw, bias, bias_f32, out, ldo, M, N, K, kb_per_split, stages, 1, g_ahead);
+                        dim3(1, z, 1), ma, mw, bias, bias_f32, out, ldo, M, N, K, kb_per_split, stages, 1);
   else
     kvad_launch(linear_tcgen05_skinny3d_kernel<MB, EPI>, dim3((N + BM - 1) / BM, z), dim3(NUM_THREADS), smem, stream, ma, mw,
-                bias, bias_f32, out, ldo, M, N, K, kb_per_split, stages, 0, g_ahead);
+                bias, bias_f32, out, ldo, M, N, K, kb_per_split, stages, 0);
   KVAD_CHECK_LAUNCH("linear_tcgen05_skinny3d");
   return KVAD_OK;
 }
@@ -965,9 +963,9 @@ int launch_skinny3d_epi(int epilogue, const CUtensorMap& ma, const CUtensorMap& 
 // form (16, 32, 64, 128, 192 or 256); bits 16-23 how many CTAs share K (residual epilogue only);
 // bits 24-25 the form: 1 wide (activation rows on the M side), 2 swapped (at most 64 rows; the
 // tile width then means weight rows per CTA, 64 or 128).
-static int linear_tcgen05_launch(const void* A, int64_t lda, const void* W, const void* bias, int bias_f32,
-                                 void* out, int64_t ldo, int M, int N, int K, int epilogue, int force,
-                                 cudaStream_t stream) {
+KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, const void* bias, int bias_f32,
+                                    void* out, int64_t ldo, int M, int N, int K, int epilogue, int force,
+                                    cudaStream_t stream) {
   KVAD_REQUIRE(M >= 0 && N > 0 && K > 0, "linear_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
   if (K % 8 != 0 || lda % 8 != 0)
     KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "linear_tcgen05: K=%d and the row stride %lld must be multiples of 8 (TMA strides are multiples of 16 bytes)", K, (long long)lda);
@@ -1009,19 +1007,34 @@ static int linear_tcgen05_launch(const void* A, int64_t lda, const void* W, cons
       // and the form above, which pipelines block by block, is the faster one: measured at 64 rows)
       // K in whole blocks of 64: few, large, three-dimensional TMA loads
       const int tiles128 = (N + BM - 1) / BM;
+      // How many CTAs share K.  A CTA whose share is one group of K blocks (W_GROUP of them, 64 KB of weights) needs
+      // so little shared memory that three fit an SM: the next launch's CTAs then sit beside this launch's, with their
+      // weights on the way while these still compute.  A CTA with two or three groups in its ring has the SM to itself,
+      // and back-to-back launches run one after the other (GPT-2 XL's sizes at 8 rows, launches back to back: the
+      // q/k/v product 9.4 us with K in four, 8.5 in seven; a residual product of the same size 6.5 -> 4.2 us).  KVAD_MAX_SPLIT_CTAS bounds the grid.
       int sp3 = 1;
+      const int one_group = (kb_all + W_GROUP - 1) / W_GROUP;     // the split that leaves every CTA one group
       if (epilogue == EPI_RESIDUAL) {
-        sp3 = force_splits > 0 ? force_splits : (148 + tiles128 - 1) / tiles128;
-        if (sp3 > 16) sp3 = 16;
+        sp3 = (148 + tiles128 - 1) / tiles128;
+        if (sp3 < one_group) sp3 = one_group;
+        if (sp3 > 32) sp3 = 32;
+        while (sp3 > 1 && tiles128 * sp3 > KVAD_MAX_SPLIT_CTAS) --sp3;
+        if (force_splits > 0) sp3 = force_splits > 32 ? 32 : force_splits;
         if (sp3 > kb_all) sp3 = kb_all;
         if (sp3 < 1) sp3 = 1;
       } else if (!g_no_cluster_k) {
-        // storing epilogues: K over a cluster of CTAs (8 at most) when that does not outnumber the SMs; measured
-        // at 8 rows and K = 768: 4.3 us whole, 4.3 in two, 3.8 in four, 3.8..4.1 in six
-        sp3 = force_splits > 0 ? force_splits : (kb_all >= 32 ? 8 : (kb_all >= 8 ? 4 : 1));
-        if (sp3 > 8) sp3 = 8;
-        if (sp3 > kb_all) sp3 = kb_all;
+        // storing epilogues: K over a cluster of CTAs (8 at most); measured at 8 rows and K = 768: 4.3 us whole,
+        // 4.3 in two, 3.8 in four, 3.8..4.1 in six
+        // (a cluster costs: at K = 512 and 118 tiles a split in three took 8.8 us against 4.8 whole - so K is split
+        // in four while that stays one wave of CTAs, and further only to reach one group a CTA)
+        sp3 = kb_all >= 8 ? 4 : 1;
         while (sp3 > 1 && tiles128 * sp3 > 160) --sp3;
+        if (one_group > 4) {
+          const int finer = one_group > 8 ? 8 : one_group;
+          if (tiles128 * finer <= KVAD_MAX_SPLIT_CTAS) sp3 = finer;
+        }
+        if (force_splits > 0) sp3 = force_splits > 8 ? 8 : force_splits;
+        if (sp3 > kb_all) sp3 = kb_all;
       }
       const int kb_per_split = (kb_all + sp3 - 1) / sp3;
       const int z = (kb_all + kb_per_split - 1) / kb_per_split;
@@ -1111,18 +1124,6 @@ static int linear_tcgen05_launch(const void* A, int64_t lda, const void* W, cons
     default: return launch_epi<256>(epilogue, ma, mw, bias, bias_f32, out, ldo, M, N, K, splits, stream);
   }
 }
-
-KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, const void* bias, int bias_f32,
-                                    void* out, int64_t ldo, int M, int N, int K, int epilogue, int force,
-                                    cudaStream_t stream) {
-  const int rc = linear_tcgen05_launch(A, lda, W, bias, bias_f32, out, ldo, M, N, K, epilogue, force, stream);
-  g_ahead = {nullptr, 0};
-  return rc;
-}
-
-// The NEXT launch of kvad_linear_tcgen05 also asks the L2 for these bytes (the weights of the product after it);
-// they must stay mapped while that launch may run, captured graphs included.  One launch uses the hint up.
-KVAD_EXPORT void kvad_linear_tcgen05_look_ahead(const void* ptr, int64_t bytes) { g_ahead = {ptr, (long long)bytes}; }
 
 // Tests: 1 keeps the swapped form on two-dimensional loads (one per K block) for every K; 2 takes the
 // grouped three-dimensional loads whenever K allows; 0 is the kernel's own choice (them, up to 16 rows).

@@ -53,12 +53,10 @@ _SIGNATURES = {
         "kvad_linear_tcgen05": [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int,
                                 c_int, c_int, c_void_p],
         "kvad_linear_tcgen05_status": [],
-        "kvad_linear_tcgen05_look_ahead": [c_void_p, c_int64],
     },
     "linear_rows": {
         "kvad_linear_rows": [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int,
                              c_void_p],
-        "kvad_linear_rows_look_ahead": [c_void_p, c_int64],
     },
     "attention_simt": {
         "kvad_attention_simt": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
@@ -223,13 +221,6 @@ class Ops:
         self.rows_linear_max = (2 if dtype == torch.bfloat16 else 16) if "linear_rows" in build.sources() else 0
         self._counters = None       # zeroed ints the decode kernel counts finished splits in (left zeroed by it)
         from . import profile
-        # Looking ahead: a product's kernel also asks the L2 for the weights of the product that FOLLOWED it the
-        # last time round (the order of a model's products repeats step after step, so it is learned, not
-        # declared), at most LOOK_AHEAD_BYTES of them.  Memory then streams through the dependent chains of
-        # the kernels in between.  KVAD_LOOK_AHEAD=0 switches it off.
-        self.look_ahead = os.environ.get("KVAD_LOOK_AHEAD", "1") != "0"
-        self._followed_by: dict[int, torch.Tensor] = {}
-        self._last_weight: Optional[torch.Tensor] = None
         if profile.enabled():       # KVAD_PROFILE=1: a table of device time per operation at exit
             profile.instrument(self)
 
@@ -237,19 +228,7 @@ class Ops:
         """Everything on the host that decides which kernels a step of a given shape launches; part of
         the key under which a step's CUDA graph is kept."""
         return (_switch_epoch, self.tensor_core_linear, self.tensor_core_prefill, self.fast_decode,
-                self.rows_linear_max, self.look_ahead)
-
-    LOOK_AHEAD_BYTES = 48 << 20
-
-    def _next_weights(self, weight) -> Optional[torch.Tensor]:
-        """Notes that `weight` follows the weight of the product before, and says what followed `weight` last time."""
-        if not self.look_ahead:
-            return None
-        last, self._last_weight = self._last_weight, weight
-        if last is not None and last is not weight:
-            self._followed_by[last.data_ptr()] = weight
-        nxt = self._followed_by.get(weight.data_ptr())
-        return nxt if nxt is not None and nxt.is_cuda else None
+                self.rows_linear_max)
 
     # -- embedding -----------------------------------------------------------------
     def embed(self, tokens, positions, wte, wpe, out) -> None:
@@ -323,9 +302,6 @@ class Ops:
                 and k % ve == 0 and lda % ve == 0 and (1 << max(0, m - 1).bit_length()) * k * a.element_size() <= 200 * 1024
                 and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and "linear_rows" in build.sources()):
             h = lib("linear_rows")
-            ahead = self._next_weights(weight)
-            if ahead is not None:
-                h.kvad_linear_rows_look_ahead(_ptr(ahead), min(ahead.numel() * ahead.element_size(), self.LOOK_AHEAD_BYTES))
             _check(h.kvad_linear_rows(self.code, _ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k, epi,
                                       _stream()), h)
             return
@@ -333,12 +309,9 @@ class Ops:
             raise KernelError("linear: the weight-streaming form takes at most 16 rows and K a multiple of a 16-byte piece, at most 1024 pieces")
         if self.tensor_core_linear and tcgen05_takes(a, weight, out, lda, ldo):
             h = lib("linear_tcgen05")
-            ahead = self._next_weights(weight)
-            if ahead is not None:
-                h.kvad_linear_tcgen05_look_ahead(_ptr(ahead), min(ahead.numel() * ahead.element_size(), self.LOOK_AHEAD_BYTES))
+            force = (int(tile) & 0xffff) | ((int(splits) & 0xff) << 16) | ({"auto": 0, "wide": 1, "swapped": 2}.get(form, 0) << 24)
             _check(h.kvad_linear_tcgen05(_ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k,
-                                         epi, (int(tile) & 0xffff) | ((int(splits) & 0xff) << 16)
-                                         | ({"auto": 0, "wide": 1, "swapped": 2}.get(form, 0) << 24), _stream()), h)
+                                         epi, force, _stream()), h)
             return
         h = lib("linear_simt")
         _check(h.kvad_linear_simt(self.code, _ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k,

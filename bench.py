@@ -293,7 +293,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=512)
-    ap.add_argument("--layers", type=int, default=GPT2_SMALL["n_layer"], help="fewer layers than GPT-2 small has (named in config)")
+    ap.add_argument("--model", default="small", choices=sorted(GPT2), help="layer sizes of the timed model; the headline is `small` (profiling runs name another)")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config); 0: all of them")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profiling)")
     ap.add_argument("--phase", default="all", choices=["all", "prefill"], help="`prefill`: only the 2 x 1024-token prefill (profiling)")
@@ -316,8 +317,9 @@ def main():
         print(f"kvad_b200 runs on one GPU; --gpus {args.gpus} is not built (multi-GPU work is out of this library's scope)")
         return 2
     warmup = max(3, args.warmup)
-    cfg = dict(GPT2_SMALL)
+    cfg = dict(GPT2[args.model])
     n_layers_full = cfg["n_layer"]
+    args.layers = args.layers or n_layers_full
     cfg["n_layer"] = args.layers
     if args.prompt_len + 1 + warmup + args.steps > cfg["n_positions"]:
         print(f"prompt {args.prompt_len} + warm-up {warmup} + steps {args.steps} exceed the context of {cfg['n_positions']}", file=sys.stderr)
@@ -348,12 +350,13 @@ def main():
     if clocks["sm_mhz"]:
         clocks["ms_per_step_x_sm_mhz"] = round(main_pt["ms_per_step"] * clocks["sm_mhz"], 2)
     out = {
-        "metric": "decode tok/s at batch 8, GPT-2 small (124M), 512-token prompts",
+        "metric": "decode tok/s at batch %d, %s, %d-token prompts"
+                  % (args.batch, {"small": "GPT-2 small (124M)", "medium": "GPT-2 medium (355M)", "xl": "GPT-2 XL (1.5B)"}[args.model], args.prompt_len),
         "value": round(main_pt["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(main_pt["ms_per_step"], 5), "rounds": main_pt["tok_s_rounds"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
         "data": "synthetic: seeded uniform-random token ids, seeded random weights",
-        "config": {"model": "gpt2-small-124M", "global_batch": args.batch, "seq_len": cfg["n_positions"],
+        "config": {"model": {"small": "gpt2-small-124M", "medium": "gpt2-medium-355M", "xl": "gpt2-xl-1.5B"}[args.model], "global_batch": args.batch, "seq_len": cfg["n_positions"],
                    "parallelism": "single-gpu", "prompt_len": args.prompt_len, "decode_steps": args.steps,
                    "n_layer": n_layers_full, "n_layer_run": args.layers, "n_embd": cfg["n_embd"], "n_head": cfg["n_head"],
                    "n_inner": cfg["n_inner"], "vocab_size": cfg["vocab_size"], "n_positions": cfg["n_positions"],

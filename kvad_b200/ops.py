@@ -381,11 +381,11 @@ class Ops:
     @staticmethod
     def decode_splits(n_rows: int, n_heads: int, table_width: int, n_sms: Optional[int] = None) -> int:
         """Into how many key ranges a decode step cuts each (row, head): as many as keep the launch one wave
-        of CTAs (2.7 an SM; three fit), six at most, one range per page at most.  Measured on a B200 at 12
+        of CTAs (2.75 an SM; three fit), six at most, one range per page at most.  Measured on a B200 at 12
         heads and ~520 keys, step time in ms by ranges: 4 rows 5: .308, 6: .311, 8: .322; 8 rows 4: .328,
         5: .353; 12 rows 2: .359, 3: .387; 16 rows 1: .394, 2: .366, 3: .405; 24 rows 1: .432, 2: .475.
         Depends on the batch's size only, never on lengths."""
-        want = (27 * (n_sms or sm_count())) // (10 * max(1, n_rows * n_heads))
+        want = (11 * (n_sms or sm_count())) // (4 * max(1, n_rows * n_heads))
         return max(1, min(want, table_width, 6))          # (the splits of a row and head form one cluster: 8 at most)
 
     def attention_decode(self, q, out, row_seq, row_pos, page_table, k_pages, v_pages, n_heads: int, scale: float,

@@ -538,7 +538,7 @@ linear_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __
 // ---------------------------------------------------------------------------------------------
 constexpr int W_GROUP = 4;          // K blocks of weights per TMA instruction and pipeline stage
 #ifndef KVAD_MAX_SPLIT_CTAS
-#define KVAD_MAX_SPLIT_CTAS 444     // CTAs of a launch whose K is split: three an SM
+#define KVAD_MAX_SPLIT_CTAS 444     // CTAs of a launch whose K is split: three times the SMs
 #endif
 
 template <int MB, int EPI>
@@ -1007,11 +1007,13 @@ KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, c
       // and the form above, which pipelines block by block, is the faster one: measured at 64 rows)
       // K in whole blocks of 64: few, large, three-dimensional TMA loads
       const int tiles128 = (N + BM - 1) / BM;
-      // How many CTAs share K.  A CTA whose share is one group of K blocks (W_GROUP of them, 64 KB of weights) needs
-      // so little shared memory that three fit an SM: the next launch's CTAs then sit beside this launch's, with their
-      // weights on the way while these still compute.  A CTA with two or three groups in its ring has the SM to itself,
-      // and back-to-back launches run one after the other (GPT-2 XL's sizes at 8 rows, launches back to back: the
-      // q/k/v product 9.4 us with K in four, 8.5 in seven; a residual product of the same size 6.5 -> 4.2 us).  KVAD_MAX_SPLIT_CTAS bounds the grid.
+      // How many CTAs share K.  Measured at GPT-2 XL's sizes and 8 rows, launches back to back in one graph: with K
+      // split until a CTA's share is ONE group of K blocks (W_GROUP of them, 64 KB of weights) a residual product
+      // of 4800 x 1600 takes 4.2 us, with two groups a CTA (K in four, one wave of CTAs) 6.5 us; the q/k/v product,
+      // whose splits are a cluster, 8.5 against 9.4 us.  Short CTAs, more of them than SMs: an SM takes up its next
+      // CTA - of this launch or, under dependent launch, of the next - as soon as one leaves, so somewhere weights
+      // are always on their way; a CTA with two or three groups in its ring holds its SM through two or three trips
+      // to memory.  KVAD_MAX_SPLIT_CTAS bounds the grid.
       int sp3 = 1;
       const int one_group = (kb_all + W_GROUP - 1) / W_GROUP;     // the split that leaves every CTA one group
       if (epilogue == EPI_RESIDUAL) {

@@ -273,6 +273,32 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ scratch,
 // one, so their first stages are requested before the dependent-launch wait.
 // Every wait is bounded; one that runs out raises g_decode_timeouts and the CTA runs on to its end.
 // ---------------------------------------------------------------------------------------------
+// The rows' queries, keys and values may come as 32-bit SUMS WITHOUT THEIR BIAS, [rows, q | k | v]: what a q/k/v
+// product leaves that splits K over CTAs and adds the shares atomically into a zeroed buffer (no cluster, no second
+// pass).  The kernel then adds the bias and rounds to the element type where it reads them, and every CTA also clears
+// its share of another buffer (`zero`: the one the NEXT such product adds into; nothing reads it meanwhile).
+struct PreQkv {
+  const float* sums;        // null: queries, keys and values come in the element type (q, k_new, v_new)
+  long long ld;
+  const void* bias;         // [q | k | v] or null
+  int bias_f32;
+  int k_off, v_off;         // columns at which keys and values start
+  float* zero;
+  long long zero_floats;
+};
+PreQkv g_pre = {nullptr, 0, nullptr, 0, 0, 0, nullptr, 0};     // for the next launch (kvad_attention_decode_pre)
+template <typename T>
+__device__ __forceinline__ void pre_piece(const PreQkv& pre, int r, int col, float* f) {
+  const float* p = pre.sums + (long long)r * pre.ld + col;
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    if (pre.bias != nullptr) f[i] += load_param(pre.bias, col + i, pre.bias_f32);
+    f[i] = to_f32(from_f32<T>(f[i]));
+  }
+}
+
 bool g_no_cluster = false;       // tests: merge the splits through global memory even where a cluster could
 bool g_force_plain = false;      // tests: keep every head size on the kernel that loads through registers
 constexpr int TMA_CONSUMER_WARPS = 4;
@@ -325,7 +351,8 @@ attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict
                             T* __restrict__ k_pages, T* __restrict__ v_pages,
                             const T* __restrict__ k_new, const T* __restrict__ v_new, int64_t ld_new,
                             float* __restrict__ scratch, int* __restrict__ counters,
-                            int n_heads, int n_kv_heads, int n_splits, float scale, int window, int cluster_merge) {
+                            int n_heads, int n_kv_heads, int n_splits, float scale, int window, int cluster_merge,
+                            const PreQkv pre) {
   using D = DecTile<T, HD>;
   constexpr int STAGES = D::STAGES;
   constexpr int CH = HD / 8;                       // lanes per key
@@ -359,6 +386,7 @@ attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict
   const int n_tiles = t_end > t_begin ? (t_end - 1) / TILE_KEYS - j0 + 1 : 0;
   const T* k_row_new = k_new ? k_new + (int64_t)r * ld_new + (int64_t)kvh * HD : nullptr;
   const T* v_row_new = v_new ? v_new + (int64_t)r * ld_new + (int64_t)kvh * HD : nullptr;
+  const bool has_new = k_row_new != nullptr || pre.sums != nullptr;      // the step's own key and value are handed in
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -393,24 +421,31 @@ attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict
       dec_bulk_load(dst + D::TILE_BYTES, vt, D::TILE_BYTES, &full_bar[s]);
     };
     // with the step's own key handed in, nothing read from the pages depends on the kernel before
-    const int pre = (k_row_new != nullptr) ? (n_tiles < STAGES ? n_tiles : STAGES) : 0;
+    const int ahead = has_new ? (n_tiles < STAGES ? n_tiles : STAGES) : 0;
     if (lane == 0)
-      for (int i = 0; i < pre; ++i) issue(i);
+      for (int i = 0; i < ahead; ++i) issue(i);
     pdl_wait();
-    if (k_row_new != nullptr && split == 0 && h % group == 0) {
+    if (has_new && split == 0 && h % group == 0) {
       // this step's key and value go to their place in the cache (no CTA of this launch reads that place)
       const int page = pages[pos / TILE_KEYS];
       const int64_t dst = (((int64_t)page * n_kv_heads + kvh) * TILE_KEYS + pos % TILE_KEYS) * HD;
       for (int idx = lane; idx < 2 * CH; idx += 32) {
         const int cc = idx % CH;
-        const T* src = (idx < CH ? k_row_new : v_row_new) + cc * 8;
         T* to = (idx < CH ? k_pages : v_pages) + dst + cc * 8;
+        if (pre.sums != nullptr) {
+          float f[8];
+          pre_piece<T>(pre, r, (idx < CH ? pre.k_off : pre.v_off) + kvh * HD + cc * 8, f);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) to[i] = src[i];
+          for (int i = 0; i < 8; ++i) to[i] = from_f32<T>(f[i]);
+        } else {
+          const T* src = (idx < CH ? k_row_new : v_row_new) + cc * 8;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) to[i] = src[i];
+        }
       }
     }
     if (lane == 0) {
-      for (int i = pre; i < n_tiles; ++i) {
+      for (int i = ahead; i < n_tiles; ++i) {
         const int s = i % STAGES;
         if (i >= STAGES && !dec_mbar_wait(&empty_bar[s], ((i / STAGES) & 1) ^ 1)) break;
         issue(i);
@@ -419,14 +454,26 @@ attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict
   } else {
     // ---- consumers
     pdl_wait();
+    if (pre.zero != nullptr) {
+      const long long n_ctas = (long long)gridDim.x * gridDim.y * gridDim.z;
+      const long long cta = ((long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+      for (long long i = cta * (TMA_CONSUMER_WARPS * 32) + tid; i < pre.zero_floats; i += n_ctas * (TMA_CONSUMER_WARPS * 32)) pre.zero[i] = 0.f;
+    }
     float qreg[8];
+    if (pre.sums != nullptr) {
+      pre_piece<T>(pre, r, h * HD + c * 8, qreg);
+    } else {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) qreg[i] = to_f32(q[(int64_t)r * ld_q + (int64_t)h * HD + c * 8 + i]);
+      for (int i = 0; i < 8; ++i) qreg[i] = to_f32(q[(int64_t)r * ld_q + (int64_t)h * HD + c * 8 + i]);
+    }
     // the step's own key and value, where they are handed in, replace what the page holds at the row's
     // position; they are fetched once, and chosen by a select where the loops below meet that position
     float k_own[8], v_own[8];
-    const bool own = k_row_new != nullptr && pos >= t_begin && pos < t_end;
-    if (own) {
+    const bool own = has_new && pos >= t_begin && pos < t_end;
+    if (own && pre.sums != nullptr) {
+      pre_piece<T>(pre, r, pre.k_off + kvh * HD + c * 8, k_own);
+      pre_piece<T>(pre, r, pre.v_off + kvh * HD + c * 8, v_own);
+    } else if (own) {
       Vec8<T>::load(k_row_new + c * 8, k_own);
       Vec8<T>::load(v_row_new + c * 8, v_own);
     } else {
@@ -667,14 +714,16 @@ int launch(const void* q, int64_t ld_q, void* out, int64_t ld_out, const int* ro
       kvad_launch_cluster(attention_decode_tma_kernel<T, HD>, grid, dim3(TMA_THREADS), D::SMEM, stream, dim3(n_splits, 1, 1),
           (const T*)q, ld_q, (T*)out, ld_out, row_seq, row_pos, page_table, table_width, (T*)const_cast<void*>(k_pages),
           (T*)const_cast<void*>(v_pages), (const T*)k_new, (const T*)v_new, ld_new, scratch, counters, n_heads, n_kv_heads,
-          n_splits, scale, window, 1);
+          n_splits, scale, window, 1, g_pre);
     } else {
       kvad_launch(attention_decode_tma_kernel<T, HD>, grid, dim3(TMA_THREADS), D::SMEM, stream,
           (const T*)q, ld_q, (T*)out, ld_out, row_seq, row_pos, page_table, table_width, (T*)const_cast<void*>(k_pages),
           (T*)const_cast<void*>(v_pages), (const T*)k_new, (const T*)v_new, ld_new, scratch, counters, n_heads, n_kv_heads,
-          n_splits, scale, window, 0);
+          n_splits, scale, window, 0, g_pre);
     }
   } else {
+    if (g_pre.sums != nullptr)
+      KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention_decode: 32-bit sums for q/k/v are taken by the TMA-fed kernel only (head size %d, page size %d)", HD, page_size);
     kvad_launch(attention_decode_kernel<T, HD>, grid, dim3(DEC_THREADS), 0, stream,
         (const T*)q, ld_q, (T*)out, ld_out, row_seq, row_pos, page_table, table_width, (T*)const_cast<void*>(k_pages),
         (T*)const_cast<void*>(v_pages), (const T*)k_new, (const T*)v_new, ld_new, scratch, counters, n_heads, n_kv_heads,
@@ -716,8 +765,13 @@ KVAD_EXPORT int kvad_attention_decode_step(int dtype, const void* q, int64_t ld_
                                            const void* v_new, int64_t ld_new, float* scratch, int* counters, int n_rows,
                                            int n_heads, int n_kv_heads, int head_dim, int page_size, int n_splits,
                                            float scale, int window, cudaStream_t stream) {
+  struct UseOnce {            // the hint of kvad_attention_decode_pre holds for this call only, however it ends
+    ~UseOnce() { g_pre = {nullptr, 0, nullptr, 0, 0, 0, nullptr, 0}; }
+  } use_once;
   KVAD_REQUIRE(n_rows >= 0 && n_heads > 0 && n_kv_heads > 0 && page_size > 0 && table_width > 0 && n_splits > 0,
                "attention_decode: bad sizes rows=%d heads=%d kv_heads=%d page=%d splits=%d", n_rows, n_heads, n_kv_heads, page_size, n_splits);
+  KVAD_REQUIRE(g_pre.sums == nullptr || (g_pre.ld % 4 == 0 && (reinterpret_cast<uintptr_t>(g_pre.sums) & 15) == 0 && g_pre.k_off % 8 == 0 && g_pre.v_off % 8 == 0 && head_dim % 8 == 0),
+               "attention_decode: the 32-bit q/k/v sums must be 16-byte aligned, with a row stride that is a multiple of 4");
   KVAD_REQUIRE(n_heads % n_kv_heads == 0, "attention_decode: %d heads do not divide into %d key/value heads", n_heads, n_kv_heads);
   KVAD_REQUIRE(n_heads <= 65535 && n_rows <= 65535, "attention_decode: %d heads x %d rows are more than one launch takes", n_heads, n_rows);
   KVAD_REQUIRE(n_splits == 1 || scratch != nullptr, "attention_decode: %d splits need scratch memory", n_splits);
@@ -745,6 +799,21 @@ KVAD_EXPORT int kvad_attention_decode_step(int dtype, const void* q, int64_t ld_
   }
 #undef KVAD_DEC_CASE
   KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention_decode: unknown dtype %d", dtype);
+}
+
+// The NEXT call of kvad_attention_decode_step takes the rows' queries, keys and values from `sums` (32-bit, [rows, ld],
+// queries from column 0, keys from k_off, values from v_off, without their bias) instead of q / k_new / v_new, adds
+// `bias` (as long as a row of sums; may be null) and rounds to the element type; it also clears `zero_floats` floats
+// at `zero` (may be null).  Head sizes and page sizes that the TMA-fed kernel does not take are refused.
+KVAD_EXPORT void kvad_attention_decode_pre(const float* sums, int64_t ld, const void* bias, int bias_f32, int k_off, int v_off,
+                                           float* zero, int64_t zero_floats) {
+  g_pre = {sums, (long long)ld, bias, bias_f32, k_off, v_off, zero, (long long)zero_floats};
+}
+
+// Whether kvad_attention_decode_pre's form is taken at this head size and page size (1) or not (0).
+KVAD_EXPORT int kvad_attention_decode_takes_pre(int dtype, int head_dim, int page_size) {
+  const bool hd_ok = head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128 || (head_dim == 256 && dtype == KVAD_DTYPE_BF16);
+  return (hd_ok && page_size == TILE_KEYS && !g_force_plain) ? 1 : 0;
 }
 
 // The cache already holds every position; a second kernel merges the splits.

@@ -211,6 +211,14 @@ void launch_layernorm_regs(const float* x, const int* row_index, const void* gai
     kvad_launch(layernorm_warp_kernel<T, 4, 4>, dim3(n_rows), dim3(128), 0, stream, x, row_index, gain, bias, params_f32, out, n_rows, width, eps);
 }
 
+// Clears device memory in stream order (a memset node when the stream is being captured).
+KVAD_EXPORT int kvad_zero_bytes(void* p, int64_t bytes, cudaStream_t stream) {
+  KVAD_REQUIRE(p != nullptr && bytes >= 0, "zero_bytes: bad arguments");
+  cudaError_t e = cudaMemsetAsync(p, 0, (size_t)bytes, stream);
+  if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "zero_bytes: %s", cudaGetErrorString(e));
+  return KVAD_OK;
+}
+
 KVAD_EXPORT int kvad_layernorm(int out_dtype, const float* x, const int* row_index, const void* gain,
                                const void* bias, int params_f32, void* out, int n_rows, int width,
                                float eps, cudaStream_t stream) {

@@ -136,6 +136,7 @@ class Model:
     # -- one step --------------------------------------------------------------------
     def forward(self, ctx) -> torch.Tensor:
         """Runs the step's rows through the model; returns float32 logits of the wanted rows."""
+        ctx.ops.begin_step()
         x = self.embedding.forward(ctx)
         for call in self.plan.order:
             self.blocks[call.layer].forward(ctx, x, call)

@@ -44,6 +44,7 @@ _SIGNATURES = {
         "kvad_layernorm": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
         "kvad_kv_store": [c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                           c_int, c_int, c_int, c_int, c_void_p],
+        "kvad_zero_bytes": [c_void_p, c_int64, c_void_p],
     },
     "linear_simt": {
         "kvad_linear_simt": [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int,
@@ -71,6 +72,8 @@ _SIGNATURES = {
         "kvad_attention_decode_step": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
                                        c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
                                        c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "kvad_attention_decode_pre": [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_void_p, c_int64],
+        "kvad_attention_decode_takes_pre": [c_int, c_int, c_int],
     },
     "sampling": {
         "kvad_sample": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -220,6 +223,11 @@ class Ops:
         # for every row count it takes (the tiled CUDA-core kernel would run one row in a tile of 64).
         self.rows_linear_max = (2 if dtype == torch.bfloat16 else 16) if "linear_rows" in build.sources() else 0
         self._counters = None       # zeroed ints the decode kernel counts finished splits in (left zeroed by it)
+        # Two 32-bit buffers [16, width] that q/k/v products of 3..16 rows add their shares of K into (see
+        # `linear_sums`); they alternate call by call, and the kernel that reads one clears the other.
+        self.qkv_sums = os.environ.get("KVAD_QKV_SUMS", "1") != "0"
+        self._sums: Optional[torch.Tensor] = None
+        self._sum_calls = 0
         from . import profile
         if profile.enabled():       # KVAD_PROFILE=1: a table of device time per operation at exit
             profile.instrument(self)
@@ -228,7 +236,14 @@ class Ops:
         """Everything on the host that decides which kernels a step of a given shape launches; part of
         the key under which a step's CUDA graph is kept."""
         return (_switch_epoch, self.tensor_core_linear, self.tensor_core_prefill, self.fast_decode,
-                self.rows_linear_max)
+                self.rows_linear_max, self.qkv_sums)
+
+    def begin_step(self) -> None:
+        """Called once before a step's first kernel (inside the capture, if the step is being captured)."""
+        self._sum_calls = 0
+        if self._sums is not None:          # the first of the two buffers starts the step clean, whatever ran before
+            h = lib("rows")
+            _check(h.kvad_zero_bytes(_ptr(self._sums), self._sums[0].numel() * 4, _stream()), h)
 
     # -- embedding -----------------------------------------------------------------
     def embed(self, tokens, positions, wte, wpe, out) -> None:
@@ -316,6 +331,63 @@ class Ops:
         h = lib("linear_simt")
         _check(h.kvad_linear_simt(self.code, _ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k,
                                   epi, _stream()), h)
+
+    def sums_take(self, m: int, weight, head_dim: int, page_size: int) -> bool:
+        """Whether a q/k/v product of `m` rows may leave 32-bit sums for the decode attention to finish (see `linear_sums`)."""
+        n, k = weight.shape
+        return bool(self.qkv_sums and self.dtype == torch.bfloat16 and self.rows_linear_max < m <= 16 and self.tensor_core_linear
+                    and self.fast_decode and k % 64 == 0 and n % 8 == 0 and weight.data_ptr() % 16 == 0 and "linear_tcgen05" in build.sources()
+                    and lib("attention_decode").kvad_attention_decode_takes_pre(self.code, int(head_dim), int(page_size)) == 1)
+
+    def linear_sums(self, a, weight):
+        """a . weight^T WITHOUT bias as 32-bit sums: the tensor-core product of a few rows splits K over CTAs, and where
+        it has to store rounded results the CTAs of a split form a cluster and meet through shared memory; where it
+        may ADD, they add their shares atomically and leave - half the time at GPT-2 XL's sizes, three quarters at
+        GPT-2 small's.  So the product adds into one of two zeroed buffers, and the kernel that reads the sums (the
+        decode attention: bias, rounding) clears the other one for the next such product; `begin_step` clears the
+        first.  Returns (the sums [rows, outputs], the buffer to clear)."""
+        m, n = a.shape[0], weight.shape[0]
+        if self._sums is None or self._sums.shape[2] < n:
+            if torch.cuda.is_current_stream_capturing():
+                raise KernelError("linear_sums: its buffers must exist before a step is captured")
+            self._sums = torch.zeros((2, 16, (n + 7) // 8 * 8), dtype=torch.float32, device=a.device)
+        which = self._sum_calls % 2
+        self._sum_calls += 1
+        out = self._sums[which, :m, :n]
+        self.linear(a, weight, None, out, "residual")
+        return out, self._sums[1 - which]
+
+    def attention_decode_sums(self, sums, bias, k_off: int, v_off: int, clear, out, row_seq, row_pos, page_table, k_pages,
+                              v_pages, n_heads: int, scale: float, window: int = 0, *, n_splits: int = 1, scratch=None) -> None:
+        """The decode attention with the rows' queries, keys and values given as `linear_sums` left them (queries from
+        column 0, keys from `k_off`, values from `v_off`; `bias` as long as a row, or None): the kernel adds the bias,
+        rounds, writes the rows' keys and values to the cache, merges its key ranges itself, and clears `clear`."""
+        _need_cuda(sums, bias, clear, out, row_seq, row_pos, page_table, k_pages, v_pages, scratch)
+        _, n_kv, page, hd = k_pages.shape
+        n = sums.shape[0]
+        ld_s, ld_o = _rows_view(sums, "q/k/v sums"), _rows_view(out, "attention output")
+        if (sums.dtype != torch.float32 or out.dtype != self.dtype or k_pages.dtype != self.dtype or out.shape != (n, n_heads * hd)
+                or k_off != n_heads * hd or v_off != k_off + n_kv * hd or sums.shape[1] != v_off + n_kv * hd):
+            raise KernelError("attention_decode_sums: sums must be float32 [rows, q | k | v] and match heads x head size")
+        bias_f32 = 0
+        if bias is not None:
+            if bias.numel() != sums.shape[1] or bias.dtype not in (torch.float32, torch.bfloat16):
+                raise KernelError("attention_decode_sums: the bias must be as long as a row of sums, float32 or bfloat16")
+            bias_f32 = 1 if bias.dtype == torch.float32 else 0
+        if n_splits > 1 and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < n * n_heads * n_splits * (hd + 2)):
+            raise KernelError("attention_decode_sums: scratch must be float32 with rows x heads x splits x (head_dim + 2) elements")
+        counters = None
+        if n_splits > 1:
+            if self._counters is None or self._counters.numel() < n * n_heads:
+                self._counters = torch.zeros(max(4096, n * n_heads), dtype=torch.int32, device=out.device)
+            counters = self._counters
+        h = lib("attention_decode")
+        h.kvad_attention_decode_pre(_ptr(sums), ld_s, _ptr(bias), bias_f32, int(k_off), int(v_off), _ptr(clear),
+                                    0 if clear is None else clear.numel())
+        _check(h.kvad_attention_decode_step(self.code, c_void_p(0), 0, _ptr(out), ld_o, _ptr(row_seq), _ptr(row_pos),
+                                            _ptr(page_table), page_table.shape[1], _ptr(k_pages), _ptr(v_pages),
+                                            c_void_p(0), c_void_p(0), 0, _ptr(scratch), _ptr(counters), n, n_heads,
+                                            n_kv, hd, page, int(n_splits), float(scale), int(window or 0), _stream()), h)
 
     # -- cache writes and attention --------------------------------------------------
     def kv_store(self, k_src, v_src, row_seq, row_pos, page_table, k_pages, v_pages) -> None:

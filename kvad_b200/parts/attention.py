@@ -54,6 +54,20 @@ class CausalSelfAttention(Mixer):
 
     def forward(self, ctx, h, residual, call):
         n = h.shape[0]
+        ops, view = ctx.ops, ctx.kv(call.cache)
+        if (ctx.batch.is_decode and call.writes_cache and self.position is None and ops.fast_decode and ops.decode_takes(self.head_dim)
+                and ops.sums_take(n, self.qkv.weight, self.head_dim, view.k_pages.shape[2])):
+            # a few single-token rows: the q/k/v product leaves 32-bit sums, and the attention kernel finishes them
+            # (bias, rounding, the cache write) where it reads them
+            sums, clear = ops.linear_sums(h, self.qkv.weight)
+            mixed = ctx.buffer((n, self.q_width))
+            splits = ops.decode_splits(n, self.n_heads, view.page_table.shape[1])
+            scratch = ctx.buffer((n * self.n_heads * splits * (self.head_dim + 2),), torch.float32) if splits > 1 else None
+            ops.attention_decode_sums(sums, self.qkv.bias, self.q_width, self.q_width + self.kv_width, clear, mixed, ctx.row_seq,
+                                      ctx.row_pos, view.page_table, view.k_pages, view.v_pages, self.n_heads, self.score_scale,
+                                      view.window or 0, n_splits=splits, scratch=scratch)
+            self.out.forward(ctx, mixed, residual, "residual")
+            return
         qkv = ctx.buffer((n, self.q_width + 2 * self.kv_width))
         self.qkv.forward(ctx, h, qkv)
         q = qkv[:, : self.q_width]

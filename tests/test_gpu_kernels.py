@@ -441,6 +441,54 @@ def _decode_split_case(ops, g, dtype, hd, n_heads, n_kv, window):
     assert int(ops._counters.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("hd,n_heads,n_kv,window", [(64, 12, 12, 0), (128, 4, 2, 0), (32, 6, 3, 70), (16, 4, 4, 0)])
+def test_attention_decode_from_sums_without_bias(hd, n_heads, n_kv, window):
+    """Queries, keys and values handed in as 32-bit sums without their bias: the kernel adds the bias and rounds,
+    so its result and what it writes to the cache equal, bit for bit, those of the same launch given the rounded
+    rows; and it leaves the other buffer cleared."""
+    from kvad_b200.ops import decode_wait_timeouts
+    g = torch.Generator().manual_seed(31 * hd + n_heads)
+    ops = Ops(torch.bfloat16)
+    lens = [700, 1, 64, 65, 130]
+    n = len(lens)
+    table, kp, vp, ks, vs = make_cache(g, "bfloat16", n, lens, n_kv, hd)
+    row_seq = torch.arange(n, dtype=torch.int32)
+    row_pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32)
+    qw, kw = n_heads * hd, n_kv * hd
+    scale = 0.9 / math.sqrt(hd)
+    sums = torch.randn(n, qw + 2 * kw, generator=g)
+    for bias in (torch.randn(qw + 2 * kw, generator=g), torch.randn(qw + 2 * kw, generator=g).bfloat16(), None):
+        rows = (sums + (bias.float() if bias is not None else 0)).bfloat16()            # what a storing product would have left
+        buffers = torch.full((2, 16, qw + 2 * kw + 8), 3.0, device="cuda")
+        buffers[0, :n, :qw + 2 * kw] = dev(sums)
+        results = []
+        for form in ("rows", "sums"):
+            kp_d, vp_d = dev(kp), dev(vp)
+            for s_, l in enumerate(lens):                      # the rows' own places hold NaN before the launch
+                kp_d[table[s_, (l - 1) // 64], :, (l - 1) % 64] = float("nan")
+                vp_d[table[s_, (l - 1) // 64], :, (l - 1) % 64] = float("nan")
+            for splits in (1, 3, 6):
+                out = torch.full((n, qw), float("nan"), device="cuda", dtype=torch.bfloat16)
+                scratch = torch.full((n * n_heads * splits * (hd + 2),), float("nan"), device="cuda")
+                if form == "rows":
+                    r_d = dev(rows)
+                    ops.attention_decode(r_d[:, :qw], out, dev(row_seq), dev(row_pos), dev(table), kp_d, vp_d, n_heads, scale, window,
+                                         n_splits=splits, scratch=scratch, k_new=r_d[:, qw:qw + kw], v_new=r_d[:, qw + kw:],
+                                         merge_in_kernel=True)
+                else:
+                    buffers[1].fill_(3.0)
+                    ops.attention_decode_sums(buffers[0, :n, :qw + 2 * kw], None if bias is None else dev(bias), qw, qw + kw, buffers[1],
+                                              out, dev(row_seq), dev(row_pos), dev(table), kp_d, vp_d, n_heads, scale, window,
+                                              n_splits=splits, scratch=scratch)
+                    assert float(buffers[1].abs().sum()) == 0.0
+                results.append((out.float().cpu(), kp_d.float().cpu(), vp_d.float().cpu()))
+        for a, b in zip(results[:3], results[3:]):                 # (places of the cache that no sequence uses hold NaN)
+            assert all(torch.equal(torch.nan_to_num(x, nan=7.0), torch.nan_to_num(y, nan=7.0)) for x, y in zip(a, b))
+        assert not torch.isnan(results[3][0]).any() and not torch.isnan(results[3][1][table[0, 699 // 64], :, 699 % 64]).any()
+    assert decode_wait_timeouts() == 0
+    assert int(ops._counters.abs().sum()) == 0
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("hd,n_heads,n_kv,window", [(64, 12, 12, 0), (128, 8, 2, 0), (32, 10, 5, 100), (256, 12, 12, 0)])
 def test_attention_decode_many_pairs(dtype, hd, n_heads, n_kv, window):

@@ -339,11 +339,12 @@ template <typename T, int HD> struct DecTile {
   static constexpr int TILE_BYTES = TILE_KEYS * HD * (int)sizeof(T);     // keys (or values) of one page and head
   static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
   static constexpr int STAGES_RAW = 65536 / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 4 ? 4 : (STAGES_RAW < 2 ? 2 : STAGES_RAW);
-  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 2 * STAGES * 8 + 128;
+  static constexpr int STAGES = STAGES_RAW > 4 ? 4 : (STAGES_RAW < 2 ? 2 : STAGES_RAW);     // the most a launch uses
+  static constexpr size_t smem(int stages) { return (size_t)stages * STAGE_BYTES + 2 * stages * 8 + 128; }
+  static constexpr size_t SMEM = smem(STAGES);
 };
 
-template <typename T, int HD>
+template <typename T, int HD, int STAGES>
 __global__ void __launch_bounds__(TMA_THREADS)
 attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict__ out, int64_t ld_out,
                             const int* __restrict__ row_seq, const int* __restrict__ row_pos,
@@ -354,7 +355,6 @@ attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict
                             int n_heads, int n_kv_heads, int n_splits, float scale, int window, int cluster_merge,
                             const PreQkv pre) {
   using D = DecTile<T, HD>;
-  constexpr int STAGES = D::STAGES;
   constexpr int CH = HD / 8;                       // lanes per key
   constexpr int KPP = 32 / CH;                     // keys a warp takes per pass
   constexpr int WARP_KEYS = TILE_KEYS / TMA_CONSUMER_WARPS;
@@ -702,25 +702,40 @@ int launch(const void* q, int64_t ld_q, void* out, int64_t ld_out, const int* ro
                             DecTile<T, HD>::SMEM <= 200 * 1024;      // two stages of 256-wide 32-bit rows do not fit
   if (tma_form && page_size == TILE_KEYS && !g_force_plain) {
     using D = DecTile<T, HD>;
-    static bool configured = false;
-    if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)D::SMEM);
-      if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "attention_decode: cannot reserve %zu bytes of shared memory: %s", D::SMEM, cudaGetErrorString(e));
-      configured = true;
-    }
     // with 2..8 splits and a merge asked for in the kernel, the splits form a cluster and merge on chip
     const bool cluster = counters != nullptr && n_splits > 1 && n_splits <= 8 && !g_no_cluster;
-    if (cluster) {
-      kvad_launch_cluster(attention_decode_tma_kernel<T, HD>, grid, dim3(TMA_THREADS), D::SMEM, stream, dim3(n_splits, 1, 1),
-          (const T*)q, ld_q, (T*)out, ld_out, row_seq, row_pos, page_table, table_width, (T*)const_cast<void*>(k_pages),
-          (T*)const_cast<void*>(v_pages), (const T*)k_new, (const T*)v_new, ld_new, scratch, counters, n_heads, n_kv_heads,
-          n_splits, scale, window, 1, g_pre);
-    } else {
-      kvad_launch(attention_decode_tma_kernel<T, HD>, grid, dim3(TMA_THREADS), D::SMEM, stream,
-          (const T*)q, ld_q, (T*)out, ld_out, row_seq, row_pos, page_table, table_width, (T*)const_cast<void*>(k_pages),
-          (T*)const_cast<void*>(v_pages), (const T*)k_new, (const T*)v_new, ld_new, scratch, counters, n_heads, n_kv_heads,
-          n_splits, scale, window, 0, g_pre);
-    }
+    // Four stages let three CTAs share an SM, three stages four.  A launch of more CTAs than three an SM but not more
+    // than four an SM runs as ONE wave with three stages (40 rows x 12 heads, ~520 keys: 17.8 -> 12.9 us; 48 rows:
+    // 18.8 -> 14.6); every other launch is faster with the deeper ring (32 rows: 10.3 against 11.5 us, 64: 21.2
+    // against 23.6).  Decided by the grid's size alone.  (The depth is a template parameter: as a run-time value it
+    // cost every launch 8 %.)
+    int sms = 148, dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long ctas = (long long)n_splits * n_heads * n_rows;
+    const bool shallow = D::STAGES == 4 && ctas > 3ll * sms && ctas <= 4ll * sms;
+    auto go = [&](auto kernel, size_t smem, bool& configured) -> int {
+      if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "attention_decode: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+      }
+      if (cluster)
+        kvad_launch_cluster(kernel, grid, dim3(TMA_THREADS), smem, stream, dim3(n_splits, 1, 1),
+            (const T*)q, ld_q, (T*)out, ld_out, row_seq, row_pos, page_table, table_width, (T*)const_cast<void*>(k_pages),
+            (T*)const_cast<void*>(v_pages), (const T*)k_new, (const T*)v_new, ld_new, scratch, counters, n_heads, n_kv_heads,
+            n_splits, scale, window, 1, g_pre);
+      else
+        kvad_launch(kernel, grid, dim3(TMA_THREADS), smem, stream,
+            (const T*)q, ld_q, (T*)out, ld_out, row_seq, row_pos, page_table, table_width, (T*)const_cast<void*>(k_pages),
+            (T*)const_cast<void*>(v_pages), (const T*)k_new, (const T*)v_new, ld_new, scratch, counters, n_heads, n_kv_heads,
+            n_splits, scale, window, 0, g_pre);
+      return KVAD_OK;
+    };
+    static bool configured_deep = false, configured_shallow = false;
+    constexpr int SHALLOW = D::STAGES == 4 ? 3 : D::STAGES;
+    const int rc = shallow ? go(attention_decode_tma_kernel<T, HD, SHALLOW>, D::smem(SHALLOW), configured_shallow)
+                           : go(attention_decode_tma_kernel<T, HD, D::STAGES>, D::SMEM, configured_deep);
+    if (rc != KVAD_OK) return rc;
   } else {
     if (g_pre.sums != nullptr)
       KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention_decode: 32-bit sums for q/k/v are taken by the TMA-fed kernel only (head size %d, page size %d)", HD, page_size);

@@ -344,7 +344,7 @@ template <typename T, int HD> struct DecTile {
   static constexpr size_t SMEM = smem(STAGES);
 };
 
-template <typename T, int HD, int STAGES>
+template <typename T, int HD, int STAGES, bool PRE>      // PRE: queries, keys and values come as PreQkv's sums
 __global__ void __launch_bounds__(TMA_THREADS)
 attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict__ out, int64_t ld_out,
                             const int* __restrict__ row_seq, const int* __restrict__ row_pos,
@@ -386,7 +386,7 @@ attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict
   const int n_tiles = t_end > t_begin ? (t_end - 1) / TILE_KEYS - j0 + 1 : 0;
   const T* k_row_new = k_new ? k_new + (int64_t)r * ld_new + (int64_t)kvh * HD : nullptr;
   const T* v_row_new = v_new ? v_new + (int64_t)r * ld_new + (int64_t)kvh * HD : nullptr;
-  const bool has_new = k_row_new != nullptr || pre.sums != nullptr;      // the step's own key and value are handed in
+  const bool has_new = PRE || k_row_new != nullptr;      // the step's own key and value are handed in
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -432,7 +432,7 @@ attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict
       for (int idx = lane; idx < 2 * CH; idx += 32) {
         const int cc = idx % CH;
         T* to = (idx < CH ? k_pages : v_pages) + dst + cc * 8;
-        if (pre.sums != nullptr) {
+        if (PRE) {
           float f[8];
           pre_piece<T>(pre, r, (idx < CH ? pre.k_off : pre.v_off) + kvh * HD + cc * 8, f);
 #pragma unroll
@@ -454,13 +454,13 @@ attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict
   } else {
     // ---- consumers
     pdl_wait();
-    if (pre.zero != nullptr) {
+    if (PRE && pre.zero != nullptr) {
       const long long n_ctas = (long long)gridDim.x * gridDim.y * gridDim.z;
       const long long cta = ((long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
       for (long long i = cta * (TMA_CONSUMER_WARPS * 32) + tid; i < pre.zero_floats; i += n_ctas * (TMA_CONSUMER_WARPS * 32)) pre.zero[i] = 0.f;
     }
     float qreg[8];
-    if (pre.sums != nullptr) {
+    if (PRE) {
       pre_piece<T>(pre, r, h * HD + c * 8, qreg);
     } else {
 #pragma unroll
@@ -470,7 +470,7 @@ attention_decode_tma_kernel(const T* __restrict__ q, int64_t ld_q, T* __restrict
     // position; they are fetched once, and chosen by a select where the loops below meet that position
     float k_own[8], v_own[8];
     const bool own = has_new && pos >= t_begin && pos < t_end;
-    if (own && pre.sums != nullptr) {
+    if (own && PRE) {
       pre_piece<T>(pre, r, pre.k_off + kvh * HD + c * 8, k_own);
       pre_piece<T>(pre, r, pre.v_off + kvh * HD + c * 8, v_own);
     } else if (own) {
@@ -731,10 +731,18 @@ int launch(const void* q, int64_t ld_q, void* out, int64_t ld_out, const int* ro
             n_splits, scale, window, 0, g_pre);
       return KVAD_OK;
     };
-    static bool configured_deep = false, configured_shallow = false;
+    static bool configured[4] = {false, false, false, false};
     constexpr int SHALLOW = D::STAGES == 4 ? 3 : D::STAGES;
-    const int rc = shallow ? go(attention_decode_tma_kernel<T, HD, SHALLOW>, D::smem(SHALLOW), configured_shallow)
-                           : go(attention_decode_tma_kernel<T, HD, D::STAGES>, D::SMEM, configured_deep);
+    constexpr bool PRE_BUILT = sizeof(T) == 2;        // the sums form is built for bfloat16 only (its only user)
+    int rc;
+    if (g_pre.sums != nullptr) {
+      if (!PRE_BUILT) KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention_decode: 32-bit sums for q/k/v are taken in bfloat16 only");
+      rc = shallow ? go(attention_decode_tma_kernel<T, HD, SHALLOW, PRE_BUILT>, D::smem(SHALLOW), configured[0])
+                   : go(attention_decode_tma_kernel<T, HD, D::STAGES, PRE_BUILT>, D::SMEM, configured[1]);
+    } else {
+      rc = shallow ? go(attention_decode_tma_kernel<T, HD, SHALLOW, false>, D::smem(SHALLOW), configured[2])
+                   : go(attention_decode_tma_kernel<T, HD, D::STAGES, false>, D::SMEM, configured[3]);
+    }
     if (rc != KVAD_OK) return rc;
   } else {
     if (g_pre.sums != nullptr)
@@ -827,8 +835,8 @@ KVAD_EXPORT void kvad_attention_decode_pre(const float* sums, int64_t ld, const 
 
 // Whether kvad_attention_decode_pre's form is taken at this head size and page size (1) or not (0).
 KVAD_EXPORT int kvad_attention_decode_takes_pre(int dtype, int head_dim, int page_size) {
-  const bool hd_ok = head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128 || (head_dim == 256 && dtype == KVAD_DTYPE_BF16);
-  return (hd_ok && page_size == TILE_KEYS && !g_force_plain) ? 1 : 0;
+  const bool hd_ok = head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128 || head_dim == 256;
+  return (dtype == KVAD_DTYPE_BF16 && hd_ok && page_size == TILE_KEYS && !g_force_plain) ? 1 : 0;
 }
 
 // The cache already holds every position; a second kernel merges the splits.

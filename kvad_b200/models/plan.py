@@ -140,4 +140,6 @@ class Model:
         x = self.embedding.forward(ctx)
         for call in self.plan.order:
             self.blocks[call.layer].forward(ctx, x, call)
-        return self.head.forward(ctx, x)
+        logits = self.head.forward(ctx, x)
+        ctx.ops.end_step()
+        return logits

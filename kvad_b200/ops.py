@@ -228,6 +228,7 @@ class Ops:
         self.qkv_sums = os.environ.get("KVAD_QKV_SUMS", "1") != "0"
         self._sums: Optional[torch.Tensor] = None
         self._sum_calls = 0
+        self._sums_open = False         # between a step's first `linear_sums` and its `end_step`
         from . import profile
         if profile.enabled():       # KVAD_PROFILE=1: a table of device time per operation at exit
             profile.instrument(self)
@@ -236,14 +237,23 @@ class Ops:
         """Everything on the host that decides which kernels a step of a given shape launches; part of
         the key under which a step's CUDA graph is kept."""
         return (_switch_epoch, self.tensor_core_linear, self.tensor_core_prefill, self.fast_decode,
-                self.rows_linear_max, self.qkv_sums)
+                self.rows_linear_max, self.qkv_sums, self.SUMS_MIN_K)
 
     def begin_step(self) -> None:
         """Called once before a step's first kernel (inside the capture, if the step is being captured)."""
+        if self._sums_open and self._sums is not None and not torch.cuda.is_current_stream_capturing():
+            self._sums.zero_()              # a step before this one was given up half-way: start clean
         self._sum_calls = 0
-        if self._sums is not None:          # the first of the two buffers starts the step clean, whatever ran before
+        self._sums_open = False
+
+    def end_step(self) -> None:
+        """Called once after a step's last kernel.  The two buffers of `linear_sums` alternate and every reader clears
+        the one it does not read, so after an even number of such products the first buffer is clean for the next
+        step; after an odd number it is cleared here."""
+        if self._sum_calls % 2 == 1:
             h = lib("rows")
             _check(h.kvad_zero_bytes(_ptr(self._sums), self._sums[0].numel() * 4, _stream()), h)
+        self._sums_open = False
 
     # -- embedding -----------------------------------------------------------------
     def embed(self, tokens, positions, wte, wpe, out) -> None:
@@ -332,20 +342,22 @@ class Ops:
         _check(h.kvad_linear_simt(self.code, _ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k,
                                   epi, _stream()), h)
 
+    SUMS_MIN_K = 1536
+
     def sums_take(self, m: int, weight, head_dim: int, page_size: int) -> bool:
-        """Whether a q/k/v product of `m` rows may leave 32-bit sums for the decode attention to finish (see `linear_sums`)."""
+        """Whether a q/k/v product of `m` rows leaves 32-bit sums for the decode attention to finish (see `linear_sums`).
+        Only where K is long (from 1536 on): there the cluster of the storing form costs most (GPT-2 XL's sizes, 8
+        rows: +4 % on the step); at K = 768 the two forms are even (+0.8 %) and at K = 1024 this one loses (-1.8 %)."""
         n, k = weight.shape
         return bool(self.qkv_sums and self.dtype == torch.bfloat16 and self.rows_linear_max < m <= 16 and self.tensor_core_linear
-                    and self.fast_decode and k % 64 == 0 and n % 8 == 0 and weight.data_ptr() % 16 == 0 and "linear_tcgen05" in build.sources()
+                    and self.fast_decode and k % 64 == 0 and k >= self.SUMS_MIN_K and n % 8 == 0 and weight.data_ptr() % 16 == 0 and "linear_tcgen05" in build.sources()
                     and lib("attention_decode").kvad_attention_decode_takes_pre(self.code, int(head_dim), int(page_size)) == 1)
 
     def linear_sums(self, a, weight):
         """a . weight^T WITHOUT bias as 32-bit sums: the tensor-core product of a few rows splits K over CTAs, and where
         it has to store rounded results the CTAs of a split form a cluster and meet through shared memory; where it
-        may ADD, they add their shares atomically and leave - half the time at GPT-2 XL's sizes, three quarters at
-        GPT-2 small's.  So the product adds into one of two zeroed buffers, and the kernel that reads the sums (the
-        decode attention: bias, rounding) clears the other one for the next such product; `begin_step` clears the
-        first.  Returns (the sums [rows, outputs], the buffer to clear)."""
+        may ADD, they add their shares atomically and leave - half the time at GPT-2 XL's sizes.  So the product adds into one of two zeroed buffers, and the kernel that reads the sums (the
+        decode attention: bias, rounding) clears the other one for the next such product (see `end_step`).  Returns (the sums [rows, outputs], the buffer to clear)."""
         m, n = a.shape[0], weight.shape[0]
         if self._sums is None or self._sums.shape[2] < n:
             if torch.cuda.is_current_stream_capturing():
@@ -353,6 +365,7 @@ class Ops:
             self._sums = torch.zeros((2, 16, (n + 7) // 8 * 8), dtype=torch.float32, device=a.device)
         which = self._sum_calls % 2
         self._sum_calls += 1
+        self._sums_open = True
         out = self._sums[which, :m, :n]
         self.linear(a, weight, None, out, "residual")
         return out, self._sums[1 - which]

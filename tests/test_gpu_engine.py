@@ -280,6 +280,42 @@ def test_no_cpu_path(model_dirs):
         ops.layernorm(x, torch.ones(8), None, 1e-5, torch.zeros(2, 8))
 
 
+@pytest.mark.parametrize("n_layer", [2, 3])
+def test_qkv_as_32_bit_sums_finished_by_the_attention_kernel(tmp_path, n_layer):
+    """The decode form that long K takes (the q/k/v product adds into a 32-bit buffer, the attention kernel adds
+    the bias, rounds and writes the cache), forced at a tiny size: 3 to 5 rows, unequal lengths, sequences that
+    end earlier, an odd number of layers (the first buffer is cleared at the step's end) and an even one, every
+    step shape kernel by kernel the first time and as a replayed graph afterwards."""
+    from kvad_b200 import Engine, write_random_model
+    from tests.plain.gpt2_plain import PlainGpt2
+    cfg = dict(model_type="gpt2", n_layer=n_layer, n_embd=128, n_head=2, n_inner=320, vocab_size=700, n_positions=512,
+               layer_norm_epsilon=1e-5, activation_function="gelu_new")
+    write_random_model(str(tmp_path), cfg, seed=77 + n_layer)
+    e, plain = Engine.from_pretrained(str(tmp_path), "bfloat16", max_tokens=2048), PlainGpt2(str(tmp_path), round_to="bfloat16")
+    e.ops.SUMS_MIN_K = 0
+    poison(e)
+    V = cfg["vocab_size"]
+    for b, prompt_lens in enumerate(([5, 11, 17], [1, 7, 30, 64, 3], [9, 2, 33, 4])):
+        seqs = [random_tokens(700 + 10 * b + i, p + 6 + 2 * i, V) for i, p in enumerate(prompt_lens)]
+        refs = [plain.logits(t) for t in seqs]
+        slots = [e.open() for _ in seqs]
+        e.step([StepEntry(s, t[:p], []) for s, t, p in zip(slots, seqs, prompt_lens)])
+        live, step = list(range(len(seqs))), 0
+        while live:
+            got = e.step([StepEntry(slots[i], [seqs[i][prompt_lens[i] + step]], [0]) for i in live]).cpu().numpy()
+            for row, i in enumerate(live):
+                pos = prompt_lens[i] + step
+                assert rel_err(got[row], refs[i][pos]) < TOL["bfloat16"], f"batch {b}: request {i} position {pos} ({len(live)} rows)"
+            step += 1
+            for i in list(live):
+                if prompt_lens[i] + step >= len(seqs[i]):
+                    e.close(slots[i])
+                    live.remove(i)
+        e.cache.book.check_all_free()
+    assert e.ops._sums is not None, "the form under test did not run"
+    assert float(e.ops._sums[0].abs().sum()) == 0.0      # clean for the next step: by the last reader, or by the step's end
+
+
 def test_dependent_launch_changes_no_result(engines, plains):
     """Kernels may start before the one before them has finished (they wait before touching its output):
     the 32-bit logits are the same bits with that switched off, and the bfloat16 ones stay right."""

@@ -320,7 +320,9 @@ class Ops:
             if not bias_f32 and bias.dtype != torch.bfloat16:
                 raise KernelError(f"linear: bias must be float32 or bfloat16, not {bias.dtype}")
         ve = 8 if self.dtype == torch.bfloat16 else 4          # elements of a 16-byte piece
-        rows_out_ok = self.dtype == torch.float32 or n <= self.ROWS_LINEAR_MAX_OUT
+        # (beyond ROWS_LINEAR_MAX_OUT outputs - the head - the tensor-core form is as fast or faster, except for one row
+        # of long K: 50257 x 1600 at one row 26 us against 44)
+        rows_out_ok = self.dtype == torch.float32 or n <= self.ROWS_LINEAR_MAX_OUT or (m == 1 and k >= 1536)
         # (by itself only up to K = 4096: beyond, one column a warp is too long a chain - measured at 1600 x 6400,
         # one row: the tensor-core form with K split over twelve CTAs is 10 % faster on the step)
         if ((form == "rows" or (form == "auto" and m <= self.rows_linear_max and rows_out_ok and k <= 4096)) and m <= 16 and k <= 1024 * ve

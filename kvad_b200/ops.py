@@ -62,6 +62,8 @@ _SIGNATURES = {
     "attention_simt": {
         "kvad_attention_simt": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "kvad_attention_tiled": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     },
     "attention_prefill": {
         "kvad_attention_prefill": [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
@@ -222,6 +224,7 @@ class Ops:
         # In 32-bit there are no tensor cores to lose to: the weight stream is the decode road of the float32 engine
         # for every row count it takes (the tiled CUDA-core kernel would run one row in a tile of 64).
         self.rows_linear_max = (2 if dtype == torch.bfloat16 else 16) if "linear_rows" in build.sources() else 0
+        self.tiled_prompt = True    # prompts that the tensor-core kernel does not take: the tiled CUDA-core kernel, not the row-by-row one
         self._counters = None       # zeroed ints the decode kernel counts finished splits in (left zeroed by it)
         # Two 32-bit buffers [16, width] that q/k/v products of 3..16 rows add their shares of K into (see
         # `linear_sums`); they alternate call by call, and the kernel that reads one clears the other.
@@ -237,7 +240,7 @@ class Ops:
         """Everything on the host that decides which kernels a step of a given shape launches; part of
         the key under which a step's CUDA graph is kept."""
         return (_switch_epoch, self.tensor_core_linear, self.tensor_core_prefill, self.fast_decode,
-                self.rows_linear_max, self.qkv_sums, self.SUMS_MIN_K)
+                self.rows_linear_max, self.qkv_sums, self.SUMS_MIN_K, self.tiled_prompt)
 
     def begin_step(self) -> None:
         """Called once before a step's first kernel (inside the capture, if the step is being captured)."""
@@ -437,6 +440,28 @@ class Ops:
         _check(h.kvad_attention_simt(self.code, _ptr(q), ld_q, _ptr(out), ld_o, _ptr(row_seq), _ptr(row_pos),
                                      _ptr(page_table), page_table.shape[1], _ptr(k_pages), _ptr(v_pages), q.shape[0],
                                      n_heads, n_kv, hd, page, float(scale), int(window or 0), _stream()), h)
+
+    def prompt_takes(self, head_dim: int, page_size: int) -> bool:
+        """Whether the tiled CUDA-core kernel for prompts takes this head size and page size."""
+        return head_dim % 4 == 0 and head_dim <= 256 and page_size == 64
+
+    def attention_prompt(self, q, out, seq_starts, kv_lens, n_seqs: int, max_new: int, page_table, k_pages, v_pages,
+                         n_heads: int, scale: float, window: int = 0) -> None:
+        """Rows of sequences packed one after another (`seq_starts`), each sequence's rows being its last positions
+        (`kv_lens` is its length after the step): causal attention on the CUDA cores in 32-bit arithmetic, a page of
+        keys brought into shared memory once for 32 rows (the float32 engine's prompts; in bfloat16 the head sizes
+        the tensor-core kernel refuses)."""
+        _need_cuda(q, out, seq_starts, kv_lens, page_table, k_pages, v_pages)
+        ld_q, ld_o = _rows_view(q, "attention queries"), _rows_view(out, "attention output")
+        _, n_kv, page, hd = k_pages.shape
+        if q.shape[1] != n_heads * hd or out.shape[1] != n_heads * hd or q.shape[0] != out.shape[0]:
+            raise KernelError("attention_prompt: queries/output do not match heads x head size")
+        if q.dtype != self.dtype or out.dtype != self.dtype or k_pages.dtype != self.dtype:
+            raise KernelError(f"attention_prompt: tensors must be {self.dtype}")
+        h = lib("attention_simt")
+        _check(h.kvad_attention_tiled(self.code, _ptr(q), ld_q, _ptr(out), ld_o, _ptr(seq_starts), _ptr(kv_lens), _ptr(page_table),
+                                      page_table.shape[1], _ptr(k_pages), _ptr(v_pages), int(n_seqs), n_heads, n_kv, hd, page,
+                                      int(max_new), float(scale), int(window or 0), _stream()), h)
 
     PREFILL_HEAD_SIZES = (16, 32, 48, 64, 80, 96, 112, 128)
 

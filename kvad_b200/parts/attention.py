@@ -99,6 +99,9 @@ class CausalSelfAttention(Mixer):
         if (not b.is_decode) and ops.tensor_core_prefill and ops.prefill_takes(hd):
             ops.attention_prefill(q, out, ctx.seq_starts, ctx.kv_lens, ctx.n_seqs, b.max_new, view.page_table,
                                   view.k_pages, view.v_pages, n_heads, scale, view.window or 0)
+        elif (not b.is_decode) and ops.tiled_prompt and ops.prompt_takes(hd, view.k_pages.shape[2]):
+            ops.attention_prompt(q, out, ctx.seq_starts, ctx.kv_lens, ctx.n_seqs, b.max_new, view.page_table,
+                                 view.k_pages, view.v_pages, n_heads, scale, view.window or 0)
         else:
             ops.attention(q, out, ctx.row_seq, ctx.row_pos, view.page_table, view.k_pages, view.v_pages,
                           n_heads, scale, view.window or 0)

@@ -22,7 +22,7 @@ import sys
 import torch
 
 #: methods of `Ops` that launch kernels, and the argument whose leading size names the shape class
-_TIMED = {"embed": 4, "layernorm": 4, "linear": 3, "kv_store": 0, "attention": 0, "attention_prefill": 0,
+_TIMED = {"embed": 4, "layernorm": 4, "linear": 3, "kv_store": 0, "attention": 0, "attention_prefill": 0, "attention_prompt": 0, "attention_decode_sums": 0,
           "attention_decode": 0, "argmax": 0, "sample": 0}
 
 _records: list = []       # (label, start event, end event)

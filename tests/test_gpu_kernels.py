@@ -603,6 +603,37 @@ def _attention_prefill_case(hd, n_heads, n_kv, window):
     assert rel(out2, ref) < KTOL["bfloat16"]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hd,n_heads,n_kv,window", [(16, 4, 4, 0), (48, 6, 2, 0), (64, 12, 12, 0), (80, 3, 1, 70), (128, 2, 2, 50),
+                                                    (256, 2, 1, 0), (20, 2, 2, 0), (36, 3, 3, 9)])
+def test_attention_prompt_tiled_on_cuda_cores(dtype, hd, n_heads, n_kv, window):
+    """The tiled CUDA-core kernel for prompts (the float32 engine's; in bfloat16 what the tensor-core kernel refuses):
+    whole prompts, prompts that continue cached positions, a single row, row counts that are no multiple of its 32
+    rows, windows that end inside a page; the pages hold NaN wherever no position lies."""
+    g = torch.Generator().manual_seed(5 * hd + n_heads + window)
+    ops = Ops(DT[dtype])
+    lens = [200, 1, 64, 65, 300, 130, 650]            # lengths after the step
+    new = [200, 1, 64, 65, 37, 129, 600]              # rows the step brings (the rest was cached before)
+    table, kp, vp, ks, vs = make_cache(g, dtype, len(lens), lens, n_kv, hd)
+    rows = [(s, p) for s, (l, n) in enumerate(zip(lens, new)) for p in range(l - n, l)]
+    row_seq = torch.tensor([r[0] for r in rows], dtype=torch.int32)
+    row_pos = torch.tensor([r[1] for r in rows], dtype=torch.int32)
+    seq_starts = torch.tensor([0] + list(np.cumsum(new)), dtype=torch.int32)
+    kv_lens = torch.tensor(lens, dtype=torch.int32)
+    q = torch.randn(len(rows), n_heads * hd + 8, generator=g).to(DT[dtype])
+    scale = 0.8 / math.sqrt(hd)
+    ref = attention_ref(q[:, :n_heads * hd], ks, vs, row_seq, row_pos, n_heads, scale, window)
+    assert ops.prompt_takes(hd, 64) and not ops.prompt_takes(hd, 32) and not ops.prompt_takes(260, 64) and not ops.prompt_takes(18, 64)
+    out = torch.full((len(rows), n_heads * hd), float("nan"), device="cuda", dtype=DT[dtype])
+    ops.attention_prompt(dev(q)[:, :n_heads * hd], out, dev(seq_starts), dev(kv_lens), len(lens), max(new), dev(table),
+                         dev(kp), dev(vp), n_heads, scale, window)
+    assert rel(out, ref) < KTOL[dtype]
+    # the row-by-row kernel agrees (to rounding in 32-bit: another order of additions)
+    out2 = torch.full_like(out, float("nan"))
+    ops.attention(dev(q)[:, :n_heads * hd], out2, dev(row_seq), dev(row_pos), dev(table), dev(kp), dev(vp), n_heads, scale, window)
+    assert rel(out2, out.float().cpu()) < (1e-5 if dtype == "float32" else KTOL[dtype])
+
+
 def test_attention_prefill_finds_one_far_key():
     g = torch.Generator().manual_seed(29)
     ops = Ops(torch.bfloat16)

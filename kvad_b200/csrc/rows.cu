@@ -126,19 +126,19 @@ __device__ __forceinline__ void load_params8(const void* p, int k0, int is_f32, 
 }
 
 // The same with the row in registers: WPR warps per row (1: widths up to NI * 256, sums met by shuffles only;
-// 4: a block of four warps per row, widths up to NI * 1024, the warps' sums added in warp order through
-// shared memory), NI chunks of 8 per thread.  Gain and bias are parameters, not the previous kernel's
+// 8: a block of eight warps per row, widths up to NI * 2048, the warps' sums added in warp order through
+// shared memory, the block walking rows blockIdx.x, blockIdx.x + gridDim.x, ...), NI chunks of 8 per thread.  Gain and bias are parameters, not the previous kernel's
 // work: they are fetched before the dependent-launch wait.
 template <typename T, int NI, int WPR>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(WPR == 1 ? 128 : 32 * WPR)
 layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
                       const void* __restrict__ gain, const void* __restrict__ bias, int params_f32,
                       T* __restrict__ out, int n_rows, int width, float eps) {
   constexpr int TPR = 32 * WPR;                     // threads per row
-  __shared__ float met[2][4];
+  __shared__ float met[2][WPR];
   pdl_launch_dependents();
   const int t = threadIdx.x % TPR, warp = threadIdx.x >> 5;
-  const int r = blockIdx.x * (4 / WPR) + threadIdx.x / TPR;
+  const int r_first = WPR == 1 ? blockIdx.x * 4 + threadIdx.x / 32 : blockIdx.x;
   float g[NI][8], b[NI][8];
 #pragma unroll
   for (int i = 0; i < NI; ++i) {
@@ -147,7 +147,9 @@ layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ row_i
     load_params8(bias, k0, params_f32, k0 < width && bias != nullptr, b[i]);
   }
   pdl_wait();
-  if (r >= n_rows) return;                          // (with four warps per row the whole block leaves)
+  // (with four warps per row a block has one row at a time and walks rows blockIdx.x, blockIdx.x + gridDim.x, ...:
+  // many rows share the parameters one block fetched)
+  for (int r = r_first; r < n_rows; r += (WPR > 1 ? (int)gridDim.x : n_rows)) {
   const float* xr = x + (int64_t)(row_index ? row_index[r] : r) * width;
   float v[NI][8];
   float sum = 0.f;
@@ -165,10 +167,13 @@ layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ row_i
     for (int u = 0; u < 8; ++u) sum += v[i][u];
   }
   sum = warp_sum(sum);
-  if (WPR == 4) {
+  if (WPR > 1) {
+    __syncthreads();                                  // the sums of the row before have been read
     if ((threadIdx.x & 31) == 0) met[0][warp] = sum;
     __syncthreads();
-    sum = ((met[0][0] + met[0][1]) + met[0][2]) + met[0][3];
+    sum = met[0][0];
+#pragma unroll
+    for (int w = 1; w < WPR; ++w) sum += met[0][w];   // in warp order
   }
   const float mean = sum / (float)width;
   float sq = 0.f;
@@ -183,10 +188,12 @@ layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ row_i
     }
   }
   sq = warp_sum(sq);
-  if (WPR == 4) {
+  if (WPR > 1) {
     if ((threadIdx.x & 31) == 0) met[1][warp] = sq;
     __syncthreads();
-    sq = ((met[1][0] + met[1][1]) + met[1][2]) + met[1][3];
+    sq = met[1][0];
+#pragma unroll
+    for (int w = 1; w < WPR; ++w) sq += met[1][w];
   }
   const float inv = 1.0f / sqrtf(sq / (float)width + eps);
   T* o = out + (int64_t)r * width;
@@ -200,6 +207,7 @@ layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ row_i
       store8(o + k0, y);
     }
   }
+  }
 }
 
 template <typename T>
@@ -207,8 +215,10 @@ void launch_layernorm_regs(const float* x, const int* row_index, const void* gai
                            int n_rows, int width, float eps, cudaStream_t stream) {
   if (width <= 1024)       // narrow rows: a warp per row
     kvad_launch(layernorm_warp_kernel<T, 4, 1>, dim3((n_rows + 3) / 4), dim3(128), 0, stream, x, row_index, gain, bias, params_f32, out, n_rows, width, eps);
-  else                     // up to 4096: four warps per row
-    kvad_launch(layernorm_warp_kernel<T, 4, 4>, dim3(n_rows), dim3(128), 0, stream, x, row_index, gain, bias, params_f32, out, n_rows, width, eps);
+  else if (width <= 2048)  // eight warps per row, 8 values a thread: few registers, so many blocks fit an SM (2048 rows of 1600: 8.9 us with four warps a row and a row a block, 7.4 with such a block walking rows, 7.2 so)
+    kvad_launch(layernorm_warp_kernel<T, 1, 8>, dim3(n_rows < 1184 ? n_rows : 1184), dim3(256), 0, stream, x, row_index, gain, bias, params_f32, out, n_rows, width, eps);
+  else                     // up to 4096
+    kvad_launch(layernorm_warp_kernel<T, 2, 8>, dim3(n_rows < 1184 ? n_rows : 1184), dim3(256), 0, stream, x, row_index, gain, bias, params_f32, out, n_rows, width, eps);
 }
 
 // Clears device memory in stream order (a memset node when the stream is being captured).

@@ -328,7 +328,10 @@ class Ops:
         rows_out_ok = self.dtype == torch.float32 or n <= self.ROWS_LINEAR_MAX_OUT or (m == 1 and k >= 1536)
         # (by itself only up to K = 4096: beyond, one column a warp is too long a chain - measured at 1600 x 6400,
         # one row: the tensor-core form with K split over twelve CTAs is 10 % faster on the step)
-        if ((form == "rows" or (form == "auto" and m <= self.rows_linear_max and rows_out_ok and k <= 4096)) and m <= 16 and k <= 1024 * ve
+        # (three and four rows too where the product STORES and K is short - there the tensor-core form needs a cluster:
+        # at GPT-2 small's sizes a step of 3 or 4 sequences 0.320 -> 0.301 ms; at K = 1024 and 1600 it loses 1..6 %)
+        rows_auto = m <= self.rows_linear_max or (m <= self.rows_linear_max + 2 and epi < 3 and k <= 768 and self.dtype == torch.bfloat16)
+        if ((form == "rows" or (form == "auto" and rows_auto and rows_out_ok and k <= 4096)) and m <= 16 and k <= 1024 * ve
                 and k % ve == 0 and lda % ve == 0 and (1 << max(0, m - 1).bit_length()) * k * a.element_size() <= 200 * 1024
                 and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and "linear_rows" in build.sources()):
             h = lib("linear_rows")

@@ -153,7 +153,8 @@ def test_linear_tensor_cores_shapes(m):
         pytest.skip("tensor-core linear kernel not built")
     from kvad_b200.ops import tcgen05_wait_timeouts
     g = torch.Generator().manual_seed(5 + m)
-    for n, k in [(768, 768), (1000, 96), (50, 320), (2304, 64), (16, 3072), (777, 200), (1031, 1600)]:
+    # (the last three: K long enough that the few-rows form splits it in 7 (a cluster), 25 and 32)
+    for n, k in [(768, 768), (1000, 96), (50, 320), (2304, 64), (16, 3072), (777, 200), (1031, 1600), (4800, 1600), (1600, 6400), (200, 8192)]:
         for epi in ("store", "gelu_tanh", "gelu_erf", "residual", "store_f32"):
             assert linear_case(ops, "bfloat16", m, n, k, epi, g) < KTOL["bfloat16"], (m, n, k, epi)
     assert linear_case(ops, "bfloat16", m, 333, 128, "store", g, bias=False, strided=True) < KTOL["bfloat16"]

@@ -295,6 +295,7 @@ class Ops:
 
     # -- linear --------------------------------------------------------------------
     ROWS_LINEAR_MAX_OUT = 8192
+    ROWS_BLOCKS_MAX = 64           # 32-bit: up to so many rows go through the weight-streaming form in blocks of 16
 
     def linear(self, a, weight, bias, out, epilogue: str = "store", *, tile: int = 0, splits: int = 0,
                form: str = "auto") -> None:
@@ -340,6 +341,20 @@ class Ops:
             return
         if form == "rows":
             raise KernelError("linear: the weight-streaming form takes at most 16 rows and K a multiple of a 16-byte piece, at most 1024 pieces")
+        if (form == "auto" and self.dtype == torch.float32 and self.rows_linear_max >= 16 and 16 < m <= self.ROWS_BLOCKS_MAX and k <= 4096
+                and k % ve == 0 and lda % ve == 0 and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and "linear_rows" in build.sources()):
+            # 32-bit, 17..64 rows: the tiled kernel would run a grid of N / 64 CTAs, each walking all of K (17 rows of
+            # 768 x 3072: 265 us); the weight-streaming form takes the rows in blocks of up to 16 instead, the later
+            # blocks finding the weights in the L2 (a decode step of 17 sequences at GPT-2 small's sizes: 6.1 -> 1.0 ms, of 64: 2.9)
+            block = 16
+            while block > 1 and block * k * 4 > 200 * 1024:
+                block //= 2
+            h = lib("linear_rows")
+            for m0 in range(0, m, block):
+                rows = min(block, m - m0)
+                _check(h.kvad_linear_rows(self.code, c_void_p(a.data_ptr() + m0 * lda * 4), lda, _ptr(weight), _ptr(bias), bias_f32,
+                                          c_void_p(out.data_ptr() + m0 * ldo * 4), ldo, rows, n, k, epi, _stream()), h)
+            return
         if self.tensor_core_linear and tcgen05_takes(a, weight, out, lda, ldo):
             h = lib("linear_tcgen05")
             force = (int(tile) & 0xffff) | ((int(splits) & 0xff) << 16) | ({"auto": 0, "wide": 1, "swapped": 2}.get(form, 0) << 24)

@@ -10,7 +10,10 @@
 // more than one split the CTA leaves an unnormalised partial result, its
 // maximum and its sum in scratch memory; the CTA that finishes last merges
 // them (or a second, tiny kernel does).  The step's own key and value can be
-// taken straight from the projection's output and written to the cache here.
+// taken straight from the projection's output and written to the cache here -
+// or, in bfloat16, from 32-bit sums that a projection whose CTAs add their shares
+// of K has left without bias (PreQkv below: bias, rounding and the cache write
+// happen where the kernel reads them).
 // All arithmetic is 32-bit; the order of operations for a row depends on the
 // number of splits and on nothing else in the batch.
 //

@@ -4,9 +4,10 @@
 // at positions max(0, pos-window+1) .. pos (window <= 0: all of them).  A block
 // serves one (row, head); it walks the keys in tiles with a running maximum and
 // sum, so the order of operations for a row depends on nothing but its own
-// keys.  This is the attention of the float32 engine for prompts and decoding
-// alike, and the bfloat16 engine's fallback for head sizes its tensor-core
-// kernels refuse.
+// keys.  It takes what the faster kernels do not: head sizes and page sizes
+// that the decode kernel or the tiled kernel below refuse, in either dtype.
+// The float32 engine's prompts (and the bfloat16 engine's, at head sizes its
+// tensor-core kernel refuses) run the tiled kernel further down.
 //
 // bisand/kvad: attend(), crates/llm/src/model/mod.rs:769-819 - score =
 // dot(q,k) * (1/sqrt(head_dim)), softmax with the maximum subtracted

@@ -149,7 +149,8 @@ layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ row_i
   pdl_wait();
   // (with four warps per row a block has one row at a time and walks rows blockIdx.x, blockIdx.x + gridDim.x, ...:
   // many rows share the parameters one block fetched)
-  for (int r = r_first; r < n_rows; r += (WPR > 1 ? (int)gridDim.x : n_rows)) {
+  if (r_first >= n_rows) return;
+  for (int r = r_first;;) {                         // (one trip with a warp per row: the loop is for the blocks that walk rows)
   const float* xr = x + (int64_t)(row_index ? row_index[r] : r) * width;
   float v[NI][8];
   float sum = 0.f;
@@ -207,6 +208,9 @@ layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ row_i
       store8(o + k0, y);
     }
   }
+  if (WPR == 1) break;
+  r += (int)gridDim.x;
+  if (r >= n_rows) break;
   }
 }
 

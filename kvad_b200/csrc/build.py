@@ -29,7 +29,7 @@ _FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-st
           "-shared", "-Xcompiler", "-fPIC"]
 _FLAGS += os.environ.get("KVAD_NVCC_FLAGS", "").split()      # more flags for every library (part of a build's name)
 #: every kernel library of the package, in the order `build_all` compiles them
-LIBRARIES = ("rows", "linear_simt", "attention_simt", "sampling", "linear_tcgen05", "linear_rows",
+LIBRARIES = ("rows", "linear_simt", "attention_simt", "sampling", "linear_tcgen05", "linear_rows", "linear_rows_f32",
              "attention_prefill", "attention_decode")
 
 _registered: dict[str, str] = {}       # kernel sources from outside the package: name -> path of the .cu file

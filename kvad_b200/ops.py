@@ -59,6 +59,10 @@ _SIGNATURES = {
         "kvad_linear_rows": [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int,
                              c_void_p],
     },
+    "linear_rows_f32": {
+        "kvad_linear_rows": [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int,
+                             c_void_p],
+    },
     "attention_simt": {
         "kvad_attention_simt": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
@@ -144,7 +148,7 @@ def lib(name: str) -> ctypes.CDLL:
 def libraries_for(dtype: torch.dtype) -> list[str]:
     """Which kernel libraries a model of this compute dtype loads."""
     names = ["rows", "linear_simt", "attention_simt", "sampling"]
-    names += [n for n in ("linear_rows", "attention_decode") if n in build.sources()]
+    names += [n for n in ("linear_rows" if dtype == torch.bfloat16 else "linear_rows_f32", "attention_decode") if n in build.sources()]
     if dtype == torch.bfloat16:
         names += [n for n in ("linear_tcgen05", "attention_prefill") if n in build.sources()]
     return names
@@ -223,7 +227,8 @@ class Ops:
         # `rows_linear_max` rows and `ROWS_LINEAR_MAX_OUT` outputs; form="rows" selects it for any count up to 16.
         # In 32-bit there are no tensor cores to lose to: the weight stream is the decode road of the float32 engine
         # for every row count it takes (the tiled CUDA-core kernel would run one row in a tile of 64).
-        self.rows_linear_max = (2 if dtype == torch.bfloat16 else 16) if "linear_rows" in build.sources() else 0
+        self._rows_lib = "linear_rows" if dtype == torch.bfloat16 else "linear_rows_f32"     # one library per element type
+        self.rows_linear_max = (2 if dtype == torch.bfloat16 else 16) if self._rows_lib in build.sources() else 0
         self.tiled_prompt = True    # prompts that the tensor-core kernel does not take: the tiled CUDA-core kernel, not the row-by-row one
         self._counters = None       # zeroed ints the decode kernel counts finished splits in (left zeroed by it)
         # Two 32-bit buffers [16, width] that q/k/v products of 3..16 rows add their shares of K into (see
@@ -334,22 +339,22 @@ class Ops:
         rows_auto = m <= self.rows_linear_max or (m <= self.rows_linear_max + 2 and epi < 3 and k <= 768 and self.dtype == torch.bfloat16)
         if ((form == "rows" or (form == "auto" and rows_auto and rows_out_ok and k <= 4096)) and m <= 16 and k <= 1024 * ve
                 and k % ve == 0 and lda % ve == 0 and (1 << max(0, m - 1).bit_length()) * k * a.element_size() <= 200 * 1024
-                and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and "linear_rows" in build.sources()):
-            h = lib("linear_rows")
+                and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and self._rows_lib in build.sources()):
+            h = lib(self._rows_lib)
             _check(h.kvad_linear_rows(self.code, _ptr(a), lda, _ptr(weight), _ptr(bias), bias_f32, _ptr(out), ldo, m, n, k, epi,
                                       _stream()), h)
             return
         if form == "rows":
             raise KernelError("linear: the weight-streaming form takes at most 16 rows and K a multiple of a 16-byte piece, at most 1024 pieces")
         if (form == "auto" and self.dtype == torch.float32 and self.rows_linear_max >= 16 and 16 < m <= self.ROWS_BLOCKS_MAX and k <= 4096
-                and k % ve == 0 and lda % ve == 0 and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and "linear_rows" in build.sources()):
+                and k % ve == 0 and lda % ve == 0 and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and self._rows_lib in build.sources()):
             # 32-bit, 17..64 rows: the tiled kernel would run a grid of N / 64 CTAs, each walking all of K (17 rows of
             # 768 x 3072: 265 us); the weight-streaming form takes the rows in blocks of up to 16 instead, the later
             # blocks finding the weights in the L2 (a decode step of 17 sequences at GPT-2 small's sizes: 6.1 -> 1.0 ms, of 64: 2.9)
             block = 16
             while block > 1 and block * k * 4 > 200 * 1024:
                 block //= 2
-            h = lib("linear_rows")
+            h = lib(self._rows_lib)
             for m0 in range(0, m, block):
                 rows = min(block, m - m0)
                 _check(h.kvad_linear_rows(self.code, c_void_p(a.data_ptr() + m0 * lda * 4), lda, _ptr(weight), _ptr(bias), bias_f32,
